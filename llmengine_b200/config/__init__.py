@@ -7,6 +7,7 @@ import os
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, Mapping, Optional, Type
 
+from .bepuzen import BepuzenConfig
 from .qwen3 import ConfigError, Qwen3Config
 from .spec import LayerRun, LayerSpec, ModelSpec, PartSpec
 
@@ -45,6 +46,8 @@ def find_architecture(name: str) -> Architecture:
 
 def config_from_dict(d: Mapping[str, Any]):
     archs = d.get("architectures")
+    if not archs and isinstance(d.get("architecture"), str):     # some designs name themselves with one string
+        archs = [d["architecture"]]
     if not archs:
         raise ConfigError("config.json lacks required key(s): architectures")
     return find_architecture(str(archs[0])).read_config(d)
@@ -63,6 +66,7 @@ def load_config(model_dir: str):
 
 
 register_architecture(Qwen3Config.ARCHITECTURE, Qwen3Config)
+register_architecture(BepuzenConfig.ARCHITECTURE, BepuzenConfig)
 
 
 @dataclass
@@ -110,6 +114,6 @@ class EngineConfig:
 
 
 __all__ = [
-    "ARCHITECTURES", "Architecture", "ConfigError", "EngineConfig", "LayerRun", "LayerSpec", "ModelSpec",
+    "ARCHITECTURES", "Architecture", "BepuzenConfig", "ConfigError", "EngineConfig", "LayerRun", "LayerSpec", "ModelSpec",
     "PartSpec", "Qwen3Config", "config_from_dict", "find_architecture", "load_config", "register_architecture",
 ]

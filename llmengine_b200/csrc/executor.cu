@@ -40,6 +40,15 @@ typedef int (*AttnDecodeFusedFn)(const LlmeFastAttnArgs*, const LlmeFusedQkv*, c
 typedef long long (*AttnScratchFn)(int, int, int);
 typedef int (*AttnTcFn)(const void*, long long, long long, const LlmeTcAttnArgs*, int, cudaStream_t);
 typedef const char* (*LastErrorFn)();
+typedef int (*XieluFn)(const void*, long long, void*, long long, int, int, int, float, float, cudaStream_t);
+typedef int (*SigmoidMulFn)(const void*, long long, const void*, long long, void*, long long, int, int, int, cudaStream_t);
+typedef int (*ResidualAddFn)(float*, const void*, const void*, int, void*, int, int, int, cudaStream_t);
+typedef int (*GeluGatherMulFn)(const void*, long long, int, const int*, const void*, int, long long, int, int, void*, long long, int, int, cudaStream_t);
+typedef int (*RmsNormAddFn)(float*, const float*, const void*, int, int, int, float, cudaStream_t);
+typedef int (*LatentPostFn)(const LlmeLatentPostArgs*, int, cudaStream_t);
+typedef int (*LatentAttnPlainFn)(const LlmeLatentAttnArgs*, int, cudaStream_t);
+typedef int (*GemmF32BatchedFn)(const float*, const void*, int, float*, int, int, int, long long, long long, long long, int, long long,
+                                long long, long long, cudaStream_t);
 
 struct Blas {
     void* lib = nullptr;
@@ -51,6 +60,9 @@ struct Blas {
     cublasStatus_t (*gemm_ex)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*, const void*,
                               cudaDataType, int, const void*, cudaDataType, int, const void*, void*, cudaDataType, int,
                               cublasComputeType_t, cublasGemmAlgo_t) = nullptr;
+    cublasStatus_t (*gemm_batched)(cublasHandle_t, cublasOperation_t, cublasOperation_t, int, int, int, const void*, const void*,
+                                   cudaDataType, int, long long, const void*, cudaDataType, int, long long, const void*, void*,
+                                   cudaDataType, int, long long, int, cublasComputeType_t, cublasGemmAlgo_t) = nullptr;
     bool load() {
         if (lib) return gemm_ex != nullptr;
         for (const char* name : {"libcublas.so.12", "libcublas.so"}) {
@@ -69,7 +81,8 @@ struct Blas {
         set_math = (decltype(set_math))dlsym(lib, "cublasSetMathMode");
         set_workspace = (decltype(set_workspace))dlsym(lib, "cublasSetWorkspace_v2");
         gemm_ex = (decltype(gemm_ex))dlsym(lib, "cublasGemmEx");
-        return create && destroy && set_stream && set_math && set_workspace && gemm_ex;
+        gemm_batched = (decltype(gemm_batched))dlsym(lib, "cublasGemmStridedBatchedEx");
+        return create && destroy && set_stream && set_math && set_workspace && gemm_ex && gemm_batched;
     }
 };
 
@@ -134,12 +147,19 @@ size_t record_size(int kind) {
         case LLME_OP_ATTEND: return sizeof(LlmeAttendOp);
         case LLME_OP_ATTENTION: return sizeof(LlmeAttentionOp);
         case LLME_OP_CALL: return sizeof(LlmeCallOp);
+        case LLME_OP_LINEAR_ACT: return sizeof(LlmeLinearActOp);
+        case LLME_OP_POINTWISE: return sizeof(LlmePointwiseOp);
+        case LLME_OP_BATCHED_LINEAR: return sizeof(LlmeBatchedLinearOp);
+        case LLME_OP_RESIDUAL_ADD: return sizeof(LlmeResidualAddOp);
+        case LLME_OP_LATENT_ATTENTION: return sizeof(LlmeLatentAttentionOp);
+        case LLME_OP_TOKEN_SIDE: return sizeof(LlmeTokenSideOp);
     }
     return 0;
 }
 const char* kind_name(int kind) {
-    static const char* names[] = {"?", "embedding", "rmsnorm", "linear", "linear_swiglu", "qkv_post", "attend", "attention", "call"};
-    return kind >= 1 && kind <= 8 ? names[kind] : names[0];
+    static const char* names[] = {"?", "embedding", "rmsnorm", "linear", "linear_swiglu", "qkv_post", "attend", "attention", "call",
+                                  "linear_act", "pointwise", "batched_linear", "residual_add", "latent_attention", "token_side"};
+    return kind >= 1 && kind <= 14 ? names[kind] : names[0];
 }
 
 constexpr int SKINNY_ROWS = 16;      // most rows the weight-streaming product takes (gemm_skinny.cu)
@@ -183,19 +203,26 @@ bool tc_fills_its_waves(const LlmeExecutor& ex, int M, int N) {
     return 10 * tiles >= 9 * waves * walkers;
 }
 
-int cublas_product(LlmeExecutor& ex, const LlmeStep& step, const void* x, long long ldx, const void* w, long long ldw, void* out,
-                   long long ldo, int out_dtype, int M, int N, int K, cudaStream_t stream) {
+// One handle for the library products of this step: the caller's, or the executor's own.
+int blas_handle(LlmeExecutor& ex, const LlmeStep& step, cudaStream_t stream, cublasHandle_t* out) {
     if (!ex.blas.load()) return ex.fail("linear: cuBLAS is not available in this process");
     cublasHandle_t h = (cublasHandle_t)step.blas;
     if (!h) {
         if (!ex.own_handle) {
             if (ex.blas.create(&ex.own_handle) != CUBLAS_STATUS_SUCCESS) return ex.fail("linear: cublasCreate failed");
-            // a workspace of its own, so that a captured step never allocates
             if (cudaMalloc(&ex.own_workspace, 32u << 20) == cudaSuccess) ex.blas.set_workspace(ex.own_handle, ex.own_workspace, 32u << 20);
         }
         h = ex.own_handle;
         ex.blas.set_stream(h, stream);
     }
+    *out = h;
+    return 0;
+}
+
+int cublas_product(LlmeExecutor& ex, const LlmeStep& step, const void* x, long long ldx, const void* w, long long ldw, void* out,
+                   long long ldo, int out_dtype, int M, int N, int K, cudaStream_t stream) {
+    cublasHandle_t h;
+    if (int rc = blas_handle(ex, step, stream, &h)) return rc;
     // partial sums are never added in bfloat16: some shapes (a few tokens, an odd width) otherwise come out a
     // thousand rounding steps off
     ex.blas.set_math(h, (cublasMath_t)(CUBLAS_DEFAULT_MATH | CUBLAS_MATH_DISALLOW_REDUCED_PRECISION_REDUCTION));
@@ -418,6 +445,96 @@ int op_attention(LlmeExecutor& ex, const LlmeAttentionOp& o, const LlmeStep& s, 
     return op_attend(ex, at, s, st);
 }
 
+int op_linear_act(LlmeExecutor& ex, const LlmeLinearActOp& o, const LlmeStep& s, cudaStream_t st) {
+    const int M = s.num_tokens;
+    if (M <= 0) return 0;
+    const LlmeLinearOp& p = o.product;
+    if (!p.out) return ex.fail("linear_act: the product needs its workspace");
+    if (int rc = product(ex, s, p.x, p.ldx, p.x_dtype, p.w, p.ldw, p.w_dtype, p.out, p.ldo, p.out_dtype, M, p.n, p.k, st)) return rc;
+    if (o.act != LLME_ACT_XIELU) return ex.fail("linear_act: unknown activation %d", o.act);
+    auto* f = (XieluFn)ex.find("xielu");
+    if (!f) return ex.fail("no xielu kernel is registered");
+    return ex.launched(f(p.out, p.ldo, o.out, o.ldo, p.out_dtype, M, p.n, o.p0, o.p1, st), "xielu");
+}
+
+int op_pointwise(LlmeExecutor& ex, const LlmePointwiseOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0) return 0;
+    if (o.what != LLME_POINTWISE_SIGMOID_MUL) return ex.fail("pointwise: unknown operation %d", o.what);
+    auto* f = (SigmoidMulFn)ex.find("sigmoid_mul");
+    if (!f) return ex.fail("no sigmoid_mul kernel is registered");
+    return ex.launched(f(o.a, o.lda, o.b, o.ldb, o.out, o.ldo, o.dtype, s.num_tokens, o.cols, st), "sigmoid_mul");
+}
+
+int op_batched_linear(LlmeExecutor& ex, const LlmeBatchedLinearOp& o, const LlmeStep& s, cudaStream_t st) {
+    const int M = s.num_tokens;
+    if (M <= 0 || o.batch <= 0) return 0;
+    if (o.x_dtype == LLME_DT_F32) {
+        auto* f = (GemmF32BatchedFn)ex.find("gemm_f32_batched");
+        if (!f) return ex.fail("batched_linear: no 32-bit batched product kernel is registered");
+        if (o.out_dtype != LLME_DT_F32) return ex.fail("batched_linear: a 32-bit product writes 32-bit output");
+        return ex.launched(f((const float*)o.x, o.w, o.w_dtype, (float*)o.out, M, o.n, o.k, o.ldx, o.ldw, o.ldo, o.batch, o.x_member,
+                             o.w_member, o.out_member, st), "gemm_f32");
+    }
+    if (o.w_dtype != LLME_DT_BF16) return ex.fail("batched_linear: bfloat16 inputs need bfloat16 weights");
+    cublasHandle_t h;
+    if (int rc = blas_handle(ex, s, st, &h)) return rc;
+    ex.blas.set_math(h, (cublasMath_t)(CUBLAS_DEFAULT_MATH | CUBLAS_MATH_DISALLOW_REDUCED_PRECISION_REDUCTION));
+    const float alpha = 1.0f, beta = 0.0f;
+    const cublasStatus_t rc = ex.blas.gemm_batched(h, CUBLAS_OP_T, CUBLAS_OP_N, o.n, M, o.k, &alpha, o.w, CUDA_R_16BF, (int)o.ldw, o.w_member,
+                                                   o.x, CUDA_R_16BF, (int)o.ldx, o.x_member, &beta, o.out,
+                                                   o.out_dtype == LLME_DT_F32 ? CUDA_R_32F : CUDA_R_16BF, (int)o.ldo, o.out_member, o.batch,
+                                                   CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+    ex.blas.set_math(h, CUBLAS_DEFAULT_MATH);
+    if (rc != CUBLAS_STATUS_SUCCESS)
+        return ex.fail("batched_linear: cublasGemmStridedBatchedEx failed with status %d for M=%d N=%d K=%d batch=%d", (int)rc, M, o.n, o.k, o.batch);
+    return 0;
+}
+
+int op_residual_add(LlmeExecutor& ex, const LlmeResidualAddOp& o, const LlmeStep& s, cudaStream_t st) {
+    auto* f = (ResidualAddFn)ex.find("residual_add");
+    if (!f) return ex.fail("no residual_add kernel is registered");
+    return ex.launched(f(o.x, o.a, o.b, o.dtype, nullptr, 0, s.num_tokens, o.size, st), "residual_add");
+}
+
+int op_latent_attention(LlmeExecutor& ex, const LlmeLatentAttentionOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0) return 0;
+    if (o.group < 0 || o.group >= s.num_groups) return ex.fail("latent attention: the step has no cache group %d", o.group);
+    const LlmeStepGroup& g = s.groups[o.group];
+    auto* post = (LatentPostFn)ex.find("latent_post");
+    if (!post) return ex.fail("no latent_post kernel is registered");
+    LlmeLatentPostArgs p = {};
+    p.kv_in = o.kv_in; p.kv_stride = o.kv_stride; p.q_rot = o.q_rot; p.q_rot_stride = o.q_rot_stride; p.q_rot_head_stride = o.q_rot_head_stride;
+    p.c_gain = o.c_gain; p.gain_dtype = o.gain_dtype; p.eps = o.eps; p.inv_freq = o.inv_freq; p.rot_dims = o.rot_dims;
+    p.positions = s.positions; p.q = o.q; p.cache = o.cache; p.slot_mapping = g.slot_mapping;
+    p.tokens = s.num_tokens; p.nh = o.nh; p.rank = o.rank; p.rot = o.rot;
+    if (int rc = ex.launched(post(&p, o.dtype, st), "latent_post")) return rc;
+    auto* plain = (LatentAttnPlainFn)ex.find("latent_attention_plain");
+    if (!plain) return ex.fail("no latent attention kernel is registered");
+    LlmeLatentAttnArgs a = {o.q, o.cache, o.out, o.sink, s.positions, s.token_request, g.block_tables, g.max_blocks, s.num_tokens,
+                            o.nh, o.rank, o.rot, g.page_size, o.scale};
+    return ex.launched(plain(&a, o.dtype, st), "latent_attention_plain");
+}
+
+int op_token_side(LlmeExecutor& ex, const LlmeTokenSideOp& o, const LlmeStep& s, cudaStream_t st) {
+    const int M = s.num_tokens;
+    if (M <= 0) return 0;
+    auto* add = (ResidualAddFn)ex.find("residual_add");
+    auto* gate = (GeluGatherMulFn)ex.find("gelu_gather_mul");
+    auto* norm = (RmsNormAddFn)ex.find("rmsnorm_add");
+    if (!add || !gate || !norm) return ex.fail("the kernels of the token side input are not registered");
+    // the stream itself is the gate's input: in the 32-bit path as it is, else a copy in the type of the products
+    const bool copy = o.act_dtype != LLME_DT_F32;
+    if (int rc = ex.launched(add(o.x, o.a, o.b, o.ab_dtype, copy ? o.xb : nullptr, o.act_dtype, M, o.size, st), "residual_add")) return rc;
+    if (int rc = product(ex, s, copy ? o.xb : (const void*)o.x, o.size, o.act_dtype, o.w_gate, o.size, o.w_dtype, o.g, o.dim, o.act_dtype, M, o.dim,
+                         o.size, st))
+        return rc;
+    if (int rc = ex.launched(gate(o.g, o.dim, o.act_dtype, s.token_ids, o.table, o.table_dtype, o.ld_table, o.offset, o.vocab, o.g, o.dim, M,
+                                  o.dim, st), "gelu_gather_mul"))
+        return rc;
+    if (int rc = product(ex, s, o.g, o.dim, o.act_dtype, o.w_proj, o.dim, o.w_dtype, o.y, o.size, LLME_DT_F32, M, o.size, o.dim, st)) return rc;
+    return ex.launched(norm(o.x, o.y, o.gain, o.gain_dtype, M, o.size, o.eps, st), "rmsnorm_add");
+}
+
 const std::map<std::string, std::vector<std::string>>& variants() {
     static const std::map<std::string, std::vector<std::string>> v = {
         {"linear", {"auto", "tcgen05", "cublas", "plain"}},
@@ -551,6 +668,12 @@ LLME_EXPORT int llme_plan_run(LlmePlan* p, const LlmeStep* step, int first, int 
             case LLME_OP_QKV_POST: rc = op_qkv_post(ex, *(const LlmeQkvPostOp*)b, s, stream); break;
             case LLME_OP_ATTEND: rc = op_attend(ex, *(const LlmeAttendOp*)b, s, stream); break;
             case LLME_OP_ATTENTION: rc = op_attention(ex, *(const LlmeAttentionOp*)b, s, stream); break;
+            case LLME_OP_LINEAR_ACT: rc = op_linear_act(ex, *(const LlmeLinearActOp*)b, s, stream); break;
+            case LLME_OP_POINTWISE: rc = op_pointwise(ex, *(const LlmePointwiseOp*)b, s, stream); break;
+            case LLME_OP_BATCHED_LINEAR: rc = op_batched_linear(ex, *(const LlmeBatchedLinearOp*)b, s, stream); break;
+            case LLME_OP_RESIDUAL_ADD: rc = op_residual_add(ex, *(const LlmeResidualAddOp*)b, s, stream); break;
+            case LLME_OP_LATENT_ATTENTION: rc = op_latent_attention(ex, *(const LlmeLatentAttentionOp*)b, s, stream); break;
+            case LLME_OP_TOKEN_SIDE: rc = op_token_side(ex, *(const LlmeTokenSideOp*)b, s, stream); break;
             case LLME_OP_CALL: {
                 const LlmeCallOp& c = *(const LlmeCallOp*)b;
                 rc = c.fn ? c.fn(c.user, step, stream) : 0;

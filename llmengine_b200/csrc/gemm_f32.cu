@@ -15,7 +15,11 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 template <typename WT>
 __global__ void __launch_bounds__(256) gemm_nt_f32_kernel(const float* __restrict__ A, const WT* __restrict__ W,
                                                           float* __restrict__ C, int M, int N, int K,
-                                                          long long lda, long long ldw, long long ldc) {
+                                                          long long lda, long long ldw, long long ldc,
+                                                          long long sa, long long sw, long long sc) {
+    A += (size_t)blockIdx.z * sa;          // one member of a batch of products per grid plane
+    W += (size_t)blockIdx.z * sw;
+    C += (size_t)blockIdx.z * sc;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tid = threadIdx.x;
@@ -65,15 +69,22 @@ __global__ void __launch_bounds__(256) gemm_nt_f32_kernel(const float* __restric
 }
 
 // A [M,K] row stride lda; W [N,K] row stride ldw (float or bfloat16); C [M,N] row stride ldc.
-LLME_API int llme_gemm_nt_f32(const float* A, const void* W, int w_dtype, float* C, int M, int N, int K,
-                              long long lda, long long ldw, long long ldc, cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return 0;
+// `batch` products in one launch: member b reads A + b * sa and W + b * sw and writes C + b * sc.
+LLME_API int llme_gemm_nt_f32_batched(const float* A, const void* W, int w_dtype, float* C, int M, int N, int K, long long lda,
+                                      long long ldw, long long ldc, int batch, long long sa, long long sw, long long sc,
+                                      cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return 0;
     if (!A || !W || !C || K <= 0) LLME_REFUSE("gemm_f32: null pointer or non-positive K");
     if (lda < K || ldw < K || ldc < N) LLME_REFUSE("gemm_f32: a row stride is shorter than the row");
-    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    if (grid.y > 65535) LLME_REFUSE("gemm_f32: M = %d needs more than 65535 row tiles", M);
-    if (w_dtype == LLME_F32) gemm_nt_f32_kernel<float><<<grid, 256, 0, stream>>>(A, (const float*)W, C, M, N, K, lda, ldw, ldc);
-    else if (w_dtype == LLME_BF16) gemm_nt_f32_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(A, (const __nv_bfloat16*)W, C, M, N, K, lda, ldw, ldc);
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+    if (grid.y > 65535 || batch > 65535) LLME_REFUSE("gemm_f32: M = %d or a batch of %d needs more than 65535 grid planes", M, batch);
+    if (w_dtype == LLME_F32) gemm_nt_f32_kernel<float><<<grid, 256, 0, stream>>>(A, (const float*)W, C, M, N, K, lda, ldw, ldc, sa, sw, sc);
+    else if (w_dtype == LLME_BF16) gemm_nt_f32_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(A, (const __nv_bfloat16*)W, C, M, N, K, lda, ldw, ldc, sa, sw, sc);
     else LLME_REFUSE("gemm_f32: unsupported weight dtype %d", w_dtype);
     LLME_LAUNCH_STATUS();
+}
+
+LLME_API int llme_gemm_nt_f32(const float* A, const void* W, int w_dtype, float* C, int M, int N, int K,
+                              long long lda, long long ldw, long long ldc, cudaStream_t stream) {
+    return llme_gemm_nt_f32_batched(A, W, w_dtype, C, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, stream);
 }

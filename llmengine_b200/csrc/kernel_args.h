@@ -46,3 +46,24 @@ typedef struct LlmeTcAttnArgs {
     int max_blocks, n_rows, nh, nkv, page_size, window;
     float scale;
 } LlmeTcAttnArgs;
+
+/* Norm of the latent, rotation of the shared key part and of the heads' rotated query parts, cache write. */
+typedef struct LlmeLatentPostArgs {
+    const void* kv_in; long long kv_stride;       /* [T, rank + rot]: raw down-projection */
+    const void* q_rot; long long q_rot_stride, q_rot_head_stride;   /* [T, nh, rot] view; nullable when rot == 0 */
+    const void* c_gain; int gain_dtype; float eps;
+    const float* inv_freq; int rot_dims;          /* rot_dims / 2 frequencies; the first rot_dims of rot are rotated */
+    const int* positions;
+    void* q;                                      /* [T, nh, rank + rot]: the last rot of every head are written */
+    void* cache; const int* slot_mapping;         /* rows of rank + rot; slot < 0: not stored */
+    int tokens, nh, rank, rot;
+} LlmeLatentPostArgs;
+
+/* Attention over cached latent rows [c | rotated key part], one row per token for all heads. */
+typedef struct LlmeLatentAttnArgs {
+    const void* q; const void* cache; void* out;  /* q [T, nh, rank + rot]; out [T, nh, rank] */
+    const float* sink;                            /* [nh] or NULL */
+    const int* positions; const int* token_request; const int* block_tables;
+    int max_blocks, tokens, nh, rank, rot, page_size;
+    float scale;
+} LlmeLatentAttnArgs;

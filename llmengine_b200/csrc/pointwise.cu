@@ -1,0 +1,214 @@
+// Memory-bound kernels of the layers that are not the pre-norm transformer body: activations with learned
+// coefficients, gates, residual adds that no norm follows, the per-layer token input, and what a latent
+// attention does between its down-projection and its cache.  All arithmetic is 32-bit; only storage may be
+// bfloat16.  Row strides are free (operands are often column ranges of a wider product), so one launch serves
+// every layout.
+#include "common.cuh"
+#include "kernel_args.h"
+
+LLME_API const char* llme_last_error() { return llme_error_buffer(); }
+
+// xIELU with its two coefficients already formed: z > 0: a_pos z^2 + z/2; z <= 0: a_neg (exp(z) - 1 - z) + z/2.
+__device__ __forceinline__ float xielu(float z, float a_pos, float a_neg) {
+    return z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
+}
+
+__device__ __forceinline__ float gelu_tanh(float z) {
+    const float k = 0.7978845608028654f;                 // sqrt(2 / pi)
+    return 0.5f * z * (1.0f + tanhf(k * (z + 0.044715f * z * z * z)));
+}
+
+__device__ __forceinline__ float sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ----------------------------------------------------------------------------- out = xielu(in)
+template <typename T>
+__global__ void xielu_kernel(const T* __restrict__ in, long long ld_in, T* __restrict__ out, long long ld_out, int cols,
+                             float a_pos, float a_neg) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* i = in + (size_t)blockIdx.x * ld_in;
+    T* o = out + (size_t)blockIdx.x * ld_out;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) o[j] = from_f32<T>(xielu(to_f32(i[j]), a_pos, a_neg));
+}
+
+LLME_API int llme_xielu(const void* in, long long ld_in, void* out, long long ld_out, int dtype, int rows, int cols,
+                        float a_pos, float a_neg, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!in || !out) LLME_REFUSE("xielu: null pointer");
+    const int threads = cols >= 1024 ? 256 : 128;
+    if (dtype == LLME_F32) llme_launch(xielu_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)in, ld_in, (float*)out, ld_out, cols, a_pos, a_neg);
+    else if (dtype == LLME_BF16) llme_launch(xielu_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (const __nv_bfloat16*)in, ld_in, (__nv_bfloat16*)out, ld_out, cols, a_pos, a_neg);
+    else LLME_REFUSE("xielu: unsupported dtype %d", dtype);
+    LLME_LAUNCH_STATUS();
+}
+
+// ----------------------------------------------------------------------------- out = a * sigmoid(b)
+template <typename T>
+__global__ void sigmoid_mul_kernel(const T* __restrict__ a, long long lda, const T* __restrict__ b, long long ldb, T* __restrict__ out,
+                                   long long ldo, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* ar = a + (size_t)blockIdx.x * lda;
+    const T* br = b + (size_t)blockIdx.x * ldb;
+    T* o = out + (size_t)blockIdx.x * ldo;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) o[j] = from_f32<T>(to_f32(ar[j]) * sigmoid(to_f32(br[j])));
+}
+
+LLME_API int llme_sigmoid_mul(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo, int dtype,
+                              int rows, int cols, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!a || !b || !out) LLME_REFUSE("sigmoid_mul: null pointer");
+    const int threads = cols >= 1024 ? 256 : 128;
+    if (dtype == LLME_F32) llme_launch(sigmoid_mul_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, cols);
+    else if (dtype == LLME_BF16) llme_launch(sigmoid_mul_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, cols);
+    else LLME_REFUSE("sigmoid_mul: unsupported dtype %d", dtype);
+    LLME_LAUNCH_STATUS();
+}
+
+// ----------------------------------------------------------------------------- x += a (+ b), optionally a copy of x in another type
+template <typename A, typename C>
+__global__ void residual_add_kernel(float* __restrict__ x, const A* __restrict__ a, const A* __restrict__ b, C* __restrict__ copy, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t base = (size_t)blockIdx.x * cols;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+        float v = to_f32(a[base + j]);
+        if (b) v += to_f32(b[base + j]);
+        v = x[base + j] + v;                 // the sublayers' contributions are summed first, then added to the stream
+        x[base + j] = v;
+        if (copy) copy[base + j] = from_f32<C>(v);
+    }
+}
+
+LLME_API int llme_residual_add(float* x, const void* a, const void* b, int ab_dtype, void* copy, int copy_dtype, int rows, int cols,
+                               cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!x || !a) LLME_REFUSE("residual_add: null pointer");
+    const int threads = cols >= 1024 ? 256 : 128;
+#define LLME_RA(A, C) llme_launch(residual_add_kernel<A, C>, dim3(rows), dim3(threads), 0, stream, x, (const A*)a, (const A*)b, (C*)copy, cols)
+    if (ab_dtype == LLME_F32 && (copy_dtype == LLME_F32 || !copy)) LLME_RA(float, float);
+    else if (ab_dtype == LLME_F32 && copy_dtype == LLME_BF16) LLME_RA(float, __nv_bfloat16);
+    else if (ab_dtype == LLME_BF16 && (copy_dtype == LLME_BF16 || !copy)) LLME_RA(__nv_bfloat16, __nv_bfloat16);
+    else if (ab_dtype == LLME_BF16 && copy_dtype == LLME_F32) LLME_RA(__nv_bfloat16, float);
+    else LLME_REFUSE("residual_add: unsupported dtypes %d / %d", ab_dtype, copy_dtype);
+#undef LLME_RA
+    LLME_LAUNCH_STATUS();
+}
+
+// ----------------------------------------------------------------------------- g = gelu_tanh(z) * table[id][offset + j]
+template <typename T, typename W>
+__global__ void gelu_gather_mul_kernel(const T* __restrict__ z, long long ldz, const int* __restrict__ ids, const W* __restrict__ table,
+                                       long long ld_table, int offset, int vocab, T* __restrict__ out, long long ldo, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int id = ids[blockIdx.x];
+    const bool ok = id >= 0 && id < vocab;
+    const W* e = table + (size_t)(ok ? id : 0) * ld_table + offset;
+    const T* zr = z + (size_t)blockIdx.x * ldz;
+    T* o = out + (size_t)blockIdx.x * ldo;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) o[j] = from_f32<T>(ok ? gelu_tanh(to_f32(zr[j])) * to_f32(e[j]) : 0.0f);
+}
+
+LLME_API int llme_gelu_gather_mul(const void* z, long long ldz, int dtype, const int* ids, const void* table, int table_dtype,
+                                  long long ld_table, int offset, int vocab, void* out, long long ldo, int rows, int cols,
+                                  cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!z || !ids || !table || !out) LLME_REFUSE("gelu_gather_mul: null pointer");
+    if (table_dtype != dtype) LLME_REFUSE("gelu_gather_mul: the table is stored in the type of the activations");
+    const int threads = cols >= 256 ? 256 : (cols >= 64 ? 64 : 32);
+    if (dtype == LLME_F32) llme_launch(gelu_gather_mul_kernel<float, float>, dim3(rows), dim3(threads), 0, stream, (const float*)z, ldz, ids, (const float*)table, ld_table, offset, vocab, (float*)out, ldo, cols);
+    else if (dtype == LLME_BF16) llme_launch(gelu_gather_mul_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (const __nv_bfloat16*)z, ldz, ids, (const __nv_bfloat16*)table, ld_table, offset, vocab, (__nv_bfloat16*)out, ldo, cols);
+    else LLME_REFUSE("gelu_gather_mul: unsupported dtype %d", dtype);
+    LLME_LAUNCH_STATUS();
+}
+
+// ----------------------------------------------------------------------------- x += y / sqrt(mean(y^2) + eps) * gain
+template <typename G>
+__global__ void rmsnorm_add_kernel(float* __restrict__ x, const float* __restrict__ y, const G* __restrict__ gain, int cols, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * cols;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+        const float v = y[base + j];
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)cols + eps);
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) x[base + j] += (y[base + j] * rinv) * to_f32(gain[j]);
+}
+
+LLME_API int llme_rmsnorm_add(float* x, const float* y, const void* gain, int gain_dtype, int rows, int cols, float eps,
+                              cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!x || !y || !gain) LLME_REFUSE("rmsnorm_add: null pointer");
+    const int threads = cols >= 1024 ? 256 : 128;
+    if (gain_dtype == LLME_F32) llme_launch(rmsnorm_add_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, y, (const float*)gain, cols, eps);
+    else if (gain_dtype == LLME_BF16) llme_launch(rmsnorm_add_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, y, (const __nv_bfloat16*)gain, cols, eps);
+    else LLME_REFUSE("rmsnorm_add: unsupported gain dtype %d", gain_dtype);
+    LLME_LAUNCH_STATUS();
+}
+
+// ----------------------------------------------------------------------------- latent: norm, rotation, cache write
+// One value of a vector whose first `dims` coordinates are rotated in rotate-half pairs (i, i + dims/2) by the angle
+// position * inv_freq[i], formed in 32-bit; coordinates from `dims` on pass unchanged.
+template <typename T>
+__device__ __forceinline__ float rotated_value(const T* __restrict__ v, int idx, int dims, const float* __restrict__ inv_freq, int position) {
+    if (idx >= dims) return to_f32(v[idx]);
+    const int half = dims >> 1, i = idx < half ? idx : idx - half;
+    const float angle = (float)position * inv_freq[i];
+    float s, c;
+    sincosf(angle, &s, &c);
+    const float u = to_f32(v[i]), w = to_f32(v[i + half]);
+    return idx < half ? u * c - w * s : w * c + u * s;
+}
+
+template <typename T, typename G>
+__global__ void latent_post_kernel(LlmeLatentPostArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, rank = a.rank, rot = a.rot, width = rank + rot;
+    const T* kv = (const T*)a.kv_in + (size_t)t * a.kv_stride;
+    const int slot = a.slot_mapping ? a.slot_mapping[t] : -1;
+    const int pos = a.positions[t];
+    T* row = (a.cache && slot >= 0) ? (T*)a.cache + (size_t)slot * width : nullptr;
+    if (row) {                                          // uniform over the block
+        float ss = 0.0f;
+        for (int j = threadIdx.x; j < rank; j += blockDim.x) {
+            const float v = to_f32(kv[j]);
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        const float rinv = 1.0f / sqrtf(ss / (float)rank + a.eps);
+        const G* gain = (const G*)a.c_gain;
+        for (int j = threadIdx.x; j < rank; j += blockDim.x) row[j] = from_f32<T>((to_f32(kv[j]) * rinv) * to_f32(gain[j]));
+        for (int j = threadIdx.x; j < rot; j += blockDim.x) row[rank + j] = from_f32<T>(rotated_value(kv + rank, j, a.rot_dims, a.inv_freq, pos));
+    }
+    if (rot > 0 && a.q_rot && a.q) {
+        const T* qr = (const T*)a.q_rot + (size_t)t * a.q_rot_stride;
+        T* q = (T*)a.q + (size_t)t * a.nh * width;
+        for (int e = threadIdx.x; e < a.nh * rot; e += blockDim.x) {
+            const int h = e / rot, j = e - h * rot;
+            q[(size_t)h * width + rank + j] = from_f32<T>(rotated_value(qr + (size_t)h * a.q_rot_head_stride, j, a.rot_dims, a.inv_freq, pos));
+        }
+    }
+}
+
+LLME_API int llme_latent_post(const LlmeLatentPostArgs* args, int dtype, cudaStream_t stream) {
+    const LlmeLatentPostArgs& a = *args;
+    if (a.tokens <= 0) return 0;
+    if (!a.kv_in || !a.c_gain || !a.positions) LLME_REFUSE("latent_post: null pointer");
+    if (a.rank <= 0 || a.rot < 0 || a.nh <= 0) LLME_REFUSE("latent_post: non-positive size");
+    if (a.rot > 0 && (!a.inv_freq || a.rot_dims <= 0 || a.rot_dims % 2 || a.rot_dims > a.rot))
+        LLME_REFUSE("latent_post: %d rotated coordinates of %d need frequencies and an even count", a.rot_dims, a.rot);
+    const int threads = 128;
+#define LLME_LP(T, G) llme_launch(latent_post_kernel<T, G>, dim3(a.tokens), dim3(threads), 0, stream, a)
+    if (dtype == LLME_F32 && a.gain_dtype == LLME_F32) LLME_LP(float, float);
+    else if (dtype == LLME_BF16 && a.gain_dtype == LLME_BF16) LLME_LP(__nv_bfloat16, __nv_bfloat16);
+    else if (dtype == LLME_BF16 && a.gain_dtype == LLME_F32) LLME_LP(__nv_bfloat16, float);
+    else LLME_REFUSE("latent_post: unsupported dtypes %d / %d", dtype, a.gain_dtype);
+#undef LLME_LP
+    LLME_LAUNCH_STATUS();
+}

@@ -79,3 +79,42 @@ class Plan:
     def call(self, fn: Callable[[Any], None], what: str = "") -> None:
         """`fn(batch)` is called in its turn with the step's `StepBatch`, on the step's stream."""
         self._add("call", fn=fn, what=what)
+
+    def linear_act(self, x: torch.Tensor, w: torch.Tensor, mid: torch.Tensor, out: torch.Tensor, act: str,
+                   params: tuple = ()) -> None:
+        """out = act(x w^T), elementwise; `mid` is the workspace of the form that runs product and activation as two
+        kernels.  Activations: "xielu" with params (a_pos, a_neg): z > 0: a_pos z^2 + z/2, else a_neg (exp(z) - 1 - z) + z/2."""
+        self._add("linear_act", x=x, w=w, mid=mid, out=out, act=act, params=tuple(float(p) for p in params))
+
+    def pointwise(self, kind: str, a: torch.Tensor, b: Optional[torch.Tensor], out: torch.Tensor) -> None:
+        """Elementwise over the step's rows (row strides free).  "sigmoid_mul": out = a * sigmoid(b)."""
+        self._add("pointwise", what=kind, a=a, b=b, out=out)
+
+    def batched_linear(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+        """out[t, b, :] = w[b] x[t, b, :] for every batch member b (one small matrix per head): x [T, B, k] and
+        out [T, B, n] are views with free row and member strides, w is [B, n, k]."""
+        self._add("batched_linear", x=x, w=w, out=out)
+
+    def residual_add(self, x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None) -> None:
+        """x += a (+ b) in 32-bit: contributions that no following norm adds."""
+        self._add("residual_add", x=x, a=a, b=b)
+
+    def latent_attention(self, *, q_rot, kv_in, c_gain, eps: float, inv_freq, rot_dims: int, q, out, cache, group: int,
+                         num_heads: int, kv_rank: int, rot_dim: int, scale: float, sink=None, scratch=None) -> None:
+        """Attention over a cache of latents, one row [c | rotated key part] per token, shared by all heads.
+        `kv_in` [T, kv_rank + rot_dim] is the raw down-projection: its first kv_rank values are RMS-normed with
+        `c_gain`, the rest rotated by the token's position (`inv_freq`: rot_dims / 2 frequencies; none: no positions),
+        and the row is stored.  `q` [T, H, kv_rank + rot_dim] holds each head's query against the latent already;
+        its last rot_dim values are filled here from `q_rot` [T, H, rot_dim] (a strided view), rotated.  Then
+        score = (q . row) * scale, causal, softmax (with `sink` [H]: the denominator also holds exp(sink_h)), and
+        out[t, h, :] = sum_j w_j c_j  [T, H, kv_rank]."""
+        self._add("latent_attention", q_rot=q_rot, kv_in=kv_in, c_gain=c_gain, eps=float(eps), inv_freq=inv_freq,
+                  rot_dims=int(rot_dims), q=q, out=out, cache=cache, group=group, num_heads=num_heads, kv_rank=kv_rank,
+                  rot_dim=rot_dim, scale=float(scale), sink=sink, scratch=scratch)
+
+    def token_side(self, *, x, a, b, table, offset: int, dim: int, w_gate, w_proj, gain, eps: float, xb, g, y) -> None:
+        """x += a (+ b); e = table[token][offset : offset + dim]; g = gelu_tanh(w_gate x) * e; y = w_proj g;
+        x += y / sqrt(mean(y^2) + eps) * gain.  `xb` [T, D], `g` [T, dim] and `y` [T, D] (32-bit) are the workspace of
+        the form that runs this as single kernels."""
+        self._add("token_side", x=x, a=a, b=b, table=table, offset=int(offset), dim=int(dim), w_gate=w_gate, w_proj=w_proj,
+                  gain=gain, eps=float(eps), xb=xb, g=g, y=y)

@@ -34,7 +34,7 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (the cache pool is made for this many)")
     ap.add_argument("--page-size", type=int, default=EngineConfig().page_size)
-    ap.add_argument("--max-requests", type=int, default=8, help="requests that may be live at once")
+    ap.add_argument("--max-requests", type=int, default=4, help="requests that may be live at once")
     ap.add_argument("--kernels", choices=["fast", "plain"], default="fast")
     args = ap.parse_args(argv)
 

@@ -67,8 +67,12 @@ typedef int (*LlmeCallFn)(void* user, const LlmeStep* step, cudaStream_t stream)
 
 enum LlmeOpKind {
     LLME_OP_EMBEDDING = 1, LLME_OP_RMSNORM, LLME_OP_LINEAR, LLME_OP_LINEAR_SWIGLU, LLME_OP_QKV_POST, LLME_OP_ATTEND,
-    LLME_OP_ATTENTION, LLME_OP_CALL
+    LLME_OP_ATTENTION, LLME_OP_CALL, LLME_OP_LINEAR_ACT, LLME_OP_POINTWISE, LLME_OP_BATCHED_LINEAR, LLME_OP_RESIDUAL_ADD,
+    LLME_OP_LATENT_ATTENTION, LLME_OP_TOKEN_SIDE
 };
+
+enum { LLME_ACT_XIELU = 1 };
+enum { LLME_POINTWISE_SIGMOID_MUL = 1 };
 
 enum { LLME_ROWS_TOKENS = 0, LLME_ROWS_LOGITS = 1 };
 
@@ -131,6 +135,58 @@ typedef struct LlmeAttentionOp {
 
 typedef struct LlmeCallOp { LlmeCallFn fn; void* user; } LlmeCallOp;
 
+/* out = act(x w^T).  LLME_ACT_XIELU with p0 = a_pos, p1 = a_neg: z > 0: a_pos z^2 + z/2, else a_neg (exp(z) - 1 - z) + z/2. */
+typedef struct LlmeLinearActOp {
+    LlmeLinearOp product;      /* its `out` is the workspace [T, n] of the form that runs product and activation apart */
+    void* out; long long ldo;  /* [T, n], the type of x */
+    int act; float p0, p1;
+} LlmeLinearActOp;
+
+/* Elementwise over the step's rows.  LLME_POINTWISE_SIGMOID_MUL: out = a * sigmoid(b). */
+typedef struct LlmePointwiseOp {
+    int what, dtype, cols;
+    const void* a; long long lda;
+    const void* b; long long ldb;
+    void* out; long long ldo;
+} LlmePointwiseOp;
+
+/* out[t, b, :] = w[b] x[t, b, :] for b < batch: one small matrix per member (a head). */
+typedef struct LlmeBatchedLinearOp {
+    const void* x; long long ldx, x_member; int x_dtype;     /* row stride, stride between members */
+    const void* w; long long ldw, w_member; int w_dtype;     /* [batch, n, k] */
+    void* out; long long ldo, out_member; int out_dtype;
+    int batch, n, k;
+} LlmeBatchedLinearOp;
+
+/* x += a (+ b): contributions that no following norm adds. */
+typedef struct LlmeResidualAddOp {
+    float* x; const void* a; const void* b; int dtype; int size;
+} LlmeResidualAddOp;
+
+/* Attention over cached latent rows [c | rotated key part] shared by all heads (csrc/attention_latent.cu), from the
+ * raw down-projection: norm of c, rotation of the key part and of the heads' rotated query parts, cache write, attention. */
+typedef struct LlmeLatentAttentionOp {
+    const void* kv_in; long long kv_stride;                   /* [T, rank + rot] */
+    const void* q_rot; long long q_rot_stride, q_rot_head_stride;   /* [T, nh, rot] view, or NULL */
+    const void* c_gain; int gain_dtype; float eps;
+    const float* inv_freq; int rot_dims;
+    void* q; void* out; int dtype;                            /* q [T, nh, rank + rot]; out [T, nh, rank] */
+    void* cache; long long cache_rows; int group;
+    int nh, rank, rot; float scale;
+    const float* sink;                                        /* [nh] or NULL */
+    float* scratch; long long scratch_floats;
+} LlmeLatentAttentionOp;
+
+/* x += a (+ b); e = table[token][offset .. offset + dim); g = gelu_tanh(w_gate x) * e; y = w_proj g;
+ * x += y / sqrt(mean(y^2) + eps) * gain. */
+typedef struct LlmeTokenSideOp {
+    float* x; const void* a; const void* b; int ab_dtype; int size;
+    const void* table; int table_dtype; long long ld_table; int offset, dim, vocab;
+    const void* w_gate; const void* w_proj; int w_dtype;      /* [dim, size], [size, dim] */
+    const void* gain; int gain_dtype; float eps;
+    void* xb; void* g; int act_dtype; float* y;               /* workspace: [T, size], [T, dim], [T, size] */
+} LlmeTokenSideOp;
+
 typedef struct LlmeExecutor LlmeExecutor;
 typedef struct LlmePlan LlmePlan;
 
@@ -138,7 +194,9 @@ LlmeExecutor* llme_executor_create(int device);
 void llme_executor_destroy(LlmeExecutor*);
 /* Entry points of the kernel libraries, by name: "embedding", "rmsnorm", "qkv_post", "swiglu", "gemm_f32",
  * "gemm_skinny", "gemm_skinny_swiglu", "gemm_tc", "gemm_tc_swiglu", "attention_plain", and per head size
- * "attention_portion/<hd>", "attention_decode/<hd>", "attention_decode_fused/<hd>", "attention_tc/<hd>". */
+ * "attention_portion/<hd>", "attention_decode/<hd>", "attention_decode_fused/<hd>", "attention_tc/<hd>"; "xielu",
+ * "sigmoid_mul", "residual_add", "gelu_gather_mul", "rmsnorm_add", "latent_post", "gemm_f32_batched",
+ * "latent_attention_plain". */
 int llme_executor_register(LlmeExecutor*, const char* name, void* entry_point);
 /* Which implementation an operation takes.  Operations and their variants:
  *   "linear":            "auto" | "tcgen05" | "cublas" | "plain"   (bfloat16 products of 128 tokens or more / all)
@@ -210,6 +268,12 @@ public:
     int add(const LlmeAttendOp& r) { return add(LLME_OP_ATTEND, &r, sizeof r); }
     int add(const LlmeAttentionOp& r) { return add(LLME_OP_ATTENTION, &r, sizeof r); }
     int add(const LlmeCallOp& r) { return add(LLME_OP_CALL, &r, sizeof r); }
+    int add(const LlmeLinearActOp& r) { return add(LLME_OP_LINEAR_ACT, &r, sizeof r); }
+    int add(const LlmePointwiseOp& r) { return add(LLME_OP_POINTWISE, &r, sizeof r); }
+    int add(const LlmeBatchedLinearOp& r) { return add(LLME_OP_BATCHED_LINEAR, &r, sizeof r); }
+    int add(const LlmeResidualAddOp& r) { return add(LLME_OP_RESIDUAL_ADD, &r, sizeof r); }
+    int add(const LlmeLatentAttentionOp& r) { return add(LLME_OP_LATENT_ATTENTION, &r, sizeof r); }
+    int add(const LlmeTokenSideOp& r) { return add(LLME_OP_TOKEN_SIDE, &r, sizeof r); }
     /* One step through the whole plan; throws with the failing record's message. */
     void run(const LlmeStep& step, cudaStream_t stream) {
         if (llme_plan_run(h_, &step, 0, -1, stream)) throw std::runtime_error(ex_.error());

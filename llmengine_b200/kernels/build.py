@@ -26,6 +26,10 @@ CSRC = os.path.join(os.path.dirname(_HERE), "csrc")
 SOURCES: Dict[str, str] = {
     "elementwise": "elementwise.cu",
     "attention_plain": "attention_plain.cu",
+    # activations, gates, the token side input and the latent attention's norm / rotation / cache write
+    "pointwise": "pointwise.cu",
+    # attention over a cache of latent rows shared by all heads
+    "attention_latent": "attention_latent.cu",
     "gemm_f32": "gemm_f32.cu",
     "sampling": "sampling.cu",
     "gemm_skinny": "gemm_skinny.cu",

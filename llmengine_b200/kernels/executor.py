@@ -11,7 +11,10 @@ import torch
 MAX_GROUPS = 8
 F32, BF16 = 0, 1
 ROWS = {"tokens": 0, "logits": 1}
-(OP_EMBEDDING, OP_RMSNORM, OP_LINEAR, OP_LINEAR_SWIGLU, OP_QKV_POST, OP_ATTEND, OP_ATTENTION, OP_CALL) = range(1, 9)
+(OP_EMBEDDING, OP_RMSNORM, OP_LINEAR, OP_LINEAR_SWIGLU, OP_QKV_POST, OP_ATTEND, OP_ATTENTION, OP_CALL, OP_LINEAR_ACT,
+ OP_POINTWISE, OP_BATCHED_LINEAR, OP_RESIDUAL_ADD, OP_LATENT_ATTENTION, OP_TOKEN_SIDE) = range(1, 15)
+ACTIVATIONS = {"xielu": 1}
+POINTWISE = {"sigmoid_mul": 1}
 
 
 def code(dt: torch.dtype) -> int:
@@ -84,6 +87,41 @@ class AttentionOp(Structure):
 
 class CallOp(Structure):
     _fields_ = [("fn", CallFn), ("user", c_void_p)]
+
+
+class LinearActOp(Structure):
+    _fields_ = [("product", LinearOp), ("out", c_void_p), ("ldo", c_longlong), ("act", c_int), ("p0", c_float), ("p1", c_float)]
+
+
+class PointwiseOp(Structure):
+    _fields_ = [("what", c_int), ("dtype", c_int), ("cols", c_int), ("a", c_void_p), ("lda", c_longlong), ("b", c_void_p),
+                ("ldb", c_longlong), ("out", c_void_p), ("ldo", c_longlong)]
+
+
+class BatchedLinearOp(Structure):
+    _fields_ = [("x", c_void_p), ("ldx", c_longlong), ("x_member", c_longlong), ("x_dtype", c_int),
+                ("w", c_void_p), ("ldw", c_longlong), ("w_member", c_longlong), ("w_dtype", c_int),
+                ("out", c_void_p), ("ldo", c_longlong), ("out_member", c_longlong), ("out_dtype", c_int),
+                ("batch", c_int), ("n", c_int), ("k", c_int)]
+
+
+class ResidualAddOp(Structure):
+    _fields_ = [("x", c_void_p), ("a", c_void_p), ("b", c_void_p), ("dtype", c_int), ("size", c_int)]
+
+
+class LatentAttentionOp(Structure):
+    _fields_ = [("kv_in", c_void_p), ("kv_stride", c_longlong), ("q_rot", c_void_p), ("q_rot_stride", c_longlong),
+                ("q_rot_head_stride", c_longlong), ("c_gain", c_void_p), ("gain_dtype", c_int), ("eps", c_float),
+                ("inv_freq", c_void_p), ("rot_dims", c_int), ("q", c_void_p), ("out", c_void_p), ("dtype", c_int),
+                ("cache", c_void_p), ("cache_rows", c_longlong), ("group", c_int), ("nh", c_int), ("rank", c_int), ("rot", c_int),
+                ("scale", c_float), ("sink", c_void_p), ("scratch", c_void_p), ("scratch_floats", c_longlong)]
+
+
+class TokenSideOp(Structure):
+    _fields_ = [("x", c_void_p), ("a", c_void_p), ("b", c_void_p), ("ab_dtype", c_int), ("size", c_int),
+                ("table", c_void_p), ("table_dtype", c_int), ("ld_table", c_longlong), ("offset", c_int), ("dim", c_int),
+                ("vocab", c_int), ("w_gate", c_void_p), ("w_proj", c_void_p), ("w_dtype", c_int), ("gain", c_void_p),
+                ("gain_dtype", c_int), ("eps", c_float), ("xb", c_void_p), ("g", c_void_p), ("act_dtype", c_int), ("y", c_void_p)]
 
 
 def declare(lib: ctypes.CDLL) -> None:
@@ -184,4 +222,55 @@ def records(op, keep: List[Any]):
                                      head_dim=hd))
         return OP_ATTENTION, AttentionOp(post, _attend_record(a), qkv.data_ptr(), qkv.stride(0),
                                          1 if a.get("cos_sin") is not None else 0)
+    if k == "linear_act":
+        x, w, mid, out = a["x"], a["w"], a["mid"], a["out"]
+        assert x.stride(1) == 1 and w.stride(1) == 1 and mid.stride(1) == 1 and out.stride(1) == 1 and w.shape[1] == x.shape[1]
+        assert mid.shape[1] == out.shape[1] == w.shape[0] and mid.dtype == out.dtype
+        p = a["params"]
+        lin = LinearOp(x.data_ptr(), x.stride(0), code(x.dtype), w.data_ptr(), w.stride(0), code(w.dtype), mid.data_ptr(),
+                       mid.stride(0), code(mid.dtype), w.shape[0], w.shape[1], ROWS["tokens"])
+        return OP_LINEAR_ACT, LinearActOp(lin, out.data_ptr(), out.stride(0), ACTIVATIONS[a["act"]], p[0] if p else 0.0,
+                                          p[1] if len(p) > 1 else 0.0)
+    if k == "pointwise":
+        x, b, out = a["a"], a["b"], a["out"]
+        assert x.stride(1) == 1 and out.stride(1) == 1 and (b is None or (b.stride(1) == 1 and b.dtype == x.dtype)) and out.dtype == x.dtype
+        return OP_POINTWISE, PointwiseOp(POINTWISE[a["what"]], code(x.dtype), out.shape[1], x.data_ptr(), x.stride(0), ptr(b),
+                                         b.stride(0) if b is not None else 0, out.data_ptr(), out.stride(0))
+    if k == "batched_linear":
+        x, w, out = a["x"], a["w"], a["out"]
+        assert x.dim() == 3 and w.dim() == 3 and out.dim() == 3 and x.stride(2) == 1 and out.stride(2) == 1 and w.is_contiguous()
+        assert x.shape[1] == w.shape[0] == out.shape[1] and x.shape[2] == w.shape[2] and out.shape[2] == w.shape[1]
+        return OP_BATCHED_LINEAR, BatchedLinearOp(x.data_ptr(), x.stride(0), x.stride(1), code(x.dtype), w.data_ptr(), w.stride(1),
+                                                  w.stride(0), code(w.dtype), out.data_ptr(), out.stride(0), out.stride(1),
+                                                  code(out.dtype), w.shape[0], w.shape[1], w.shape[2])
+    if k == "residual_add":
+        x, u, v = a["x"], a["a"], a["b"]
+        assert x.dtype == torch.float32 and x.is_contiguous() and u.is_contiguous() and u.shape == x.shape
+        assert v is None or (v.is_contiguous() and v.dtype == u.dtype and v.shape == x.shape)
+        return OP_RESIDUAL_ADD, ResidualAddOp(x.data_ptr(), u.data_ptr(), ptr(v), code(u.dtype), x.shape[1])
+    if k == "latent_attention":
+        q, out, cache, kv, qr, gain = a["q"], a["out"], a["cache"], a["kv_in"], a["q_rot"], a["c_gain"]
+        H, r, dr = a["num_heads"], a["kv_rank"], a["rot_dim"]
+        assert q.dtype == out.dtype == cache.dtype == kv.dtype and q.is_contiguous() and out.is_contiguous() and cache.is_contiguous()
+        assert q.shape[1] == H * (r + dr) and out.shape[1] == H * r and cache.shape[-1] == r + dr and kv.stride(1) == 1
+        assert (qr is None) == (dr == 0) and (qr is None or (qr.dtype == q.dtype and qr.stride(2) == 1 and tuple(qr.shape[1:]) == (H, dr)))
+        freq, sink, scratch = a["inv_freq"], a["sink"], a.get("scratch")
+        assert freq is None or (freq.dtype == torch.float32 and freq.numel() * 2 == a["rot_dims"])
+        assert sink is None or (sink.dtype == torch.float32 and sink.numel() == H)
+        return OP_LATENT_ATTENTION, LatentAttentionOp(
+            kv.data_ptr(), kv.stride(0), ptr(qr), qr.stride(0) if qr is not None else 0, qr.stride(1) if qr is not None else 0,
+            gain.data_ptr(), code(gain.dtype), a["eps"], ptr(freq), a["rot_dims"], q.data_ptr(), out.data_ptr(), code(q.dtype),
+            cache.data_ptr(), cache.shape[0] * cache.shape[1], a["group"], H, r, dr, a["scale"], ptr(sink), ptr(scratch),
+            scratch.numel() if scratch is not None else 0)
+    if k == "token_side":
+        x, u, v, table, wg, wp, gain, xb, g, y = (a[n] for n in ("x", "a", "b", "table", "w_gate", "w_proj", "gain", "xb", "g", "y"))
+        D, dim = x.shape[1], a["dim"]
+        assert x.dtype == y.dtype == torch.float32 and all(t.is_contiguous() for t in (x, u, table, wg, wp, gain, xb, g, y))
+        assert v is None or (v.is_contiguous() and v.dtype == u.dtype)
+        assert tuple(wg.shape) == (dim, D) and tuple(wp.shape) == (D, dim) and wg.dtype == wp.dtype and xb.dtype == g.dtype == table.dtype
+        assert xb.shape[1] == D and g.shape[1] == dim and y.shape[1] == D and gain.numel() == D
+        return OP_TOKEN_SIDE, TokenSideOp(x.data_ptr(), u.data_ptr(), ptr(v), code(u.dtype), D, table.data_ptr(), code(table.dtype),
+                                          table.stride(0), a["offset"], dim, table.shape[0], wg.data_ptr(), wp.data_ptr(),
+                                          code(wg.dtype), gain.data_ptr(), code(gain.dtype), a["eps"], xb.data_ptr(), g.data_ptr(),
+                                          code(g.dtype), y.data_ptr())
     raise ValueError(f"the executor has no record for the operation {k!r}")

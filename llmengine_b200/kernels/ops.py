@@ -176,7 +176,11 @@ class CudaOps:
     _ENTRY_POINTS = {
         "elementwise": {"embedding": "llme_embedding", "rmsnorm": "llme_rmsnorm", "qkv_post": "llme_qkv_post",
                         "swiglu": "llme_swiglu"},
-        "gemm_f32": {"gemm_f32": "llme_gemm_nt_f32"},
+        "gemm_f32": {"gemm_f32": "llme_gemm_nt_f32", "gemm_f32_batched": "llme_gemm_nt_f32_batched"},
+        "pointwise": {"xielu": "llme_xielu", "sigmoid_mul": "llme_sigmoid_mul", "residual_add": "llme_residual_add",
+                      "gelu_gather_mul": "llme_gelu_gather_mul", "rmsnorm_add": "llme_rmsnorm_add",
+                      "latent_post": "llme_latent_post"},
+        "attention_latent": {"latent_attention_plain": "llme_latent_attention_plain"},
         "gemm_skinny": {"gemm_skinny": "llme_gemm_skinny_bf16", "gemm_skinny_swiglu": "llme_gemm_skinny_swiglu_bf16"},
         "gemm_tcgen05": {"gemm_tc": "llme_gemm_tc_bf16", "gemm_tc_swiglu": "llme_gemm_tc_swiglu_bf16"},
         "attention_plain": {"attention_plain": "llme_attention_plain"},
@@ -210,7 +214,18 @@ class CudaOps:
             a = op.a
             if op.kind in ("embedding", "rmsnorm", "qkv_post", "attention"):
                 want("elementwise")
-            if op.kind in ("linear", "linear_swiglu"):
+            if op.kind in ("linear_act", "pointwise", "residual_add", "latent_attention", "token_side"):
+                want("pointwise")
+            if op.kind == "latent_attention":
+                want("attention_latent")
+            if op.kind == "batched_linear" and a["x"].dtype == torch.float32:
+                want("gemm_f32")
+            if op.kind == "token_side":
+                if a["w_gate"].dtype == torch.float32:
+                    want("gemm_f32")
+                elif self.chosen("linear") != "plain" and self.chosen("linear.decode") != "cublas":
+                    want("gemm_skinny")
+            if op.kind in ("linear", "linear_swiglu", "linear_act"):
                 if a["x"].dtype == torch.float32:
                     want("gemm_f32")
                 elif self.chosen("linear") != "plain":

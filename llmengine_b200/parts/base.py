@@ -53,7 +53,7 @@ class WeightSpec:
     """One tensor a part needs.  `role` decides the stored type: a "matrix" is an operand of a
     matrix product and takes the engine's compute type; a "vector" keeps 32-bit storage when the
     file has it so (else the file's 16-bit type); a "table" is integer data kept as int32.
-    `init` is used by the random-weights mode: "normal" ~ N(0, 0.02), "gain" ~ 1 + N(0, 0.1)."""
+    `init` is used by the random-weights mode: "normal" ~ N(0, 0.02), "gain" ~ 1 + N(0, 0.1), "unit" ~ N(0, 1)."""
 
     shape: Tuple[int, ...]
     role: str = "matrix"
@@ -136,6 +136,10 @@ class Part:
         """Receives the tensors named by `weight_specs`, already on the device."""
 
     def name(self, leaf: str) -> str:
+        """The full name of this part's tensor `leaf`; an empty leaf is the prefix itself (a part with one tensor
+        whose file names it without a suffix)."""
+        if not leaf:
+            return self.prefix
         return f"{self.prefix}.{leaf}" if self.prefix else leaf
 
     def tied_tensors(self) -> Dict[str, str]:
@@ -305,6 +309,11 @@ def emit_head(plan, part: Part, h: torch.Tensor) -> None:
 _REGISTRIES: Dict[str, Dict[str, Callable[..., Part]]] = {
     c: {} for c in ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
 }
+
+
+def register_category(category: str) -> None:
+    """A further category of parts (a kind of sublayer that only some block arrangements ask for)."""
+    _REGISTRIES.setdefault(category, {})
 
 
 def register_part(category: str, kind: str) -> Callable[[Callable[..., Part]], Callable[..., Part]]:

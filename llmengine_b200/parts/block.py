@@ -62,3 +62,72 @@ class PreNormResidualBlock(Part):
         x, out = self.emit(plan, x, delta, cache)
         run_alone(self.rt, plan, batch)
         return x, out[: x.shape[0]]
+
+
+@register_part("block", "parallel_residual")
+class ParallelResidualBlock(Part):
+    """h = norm(x);  x = x + (mixer(h) + feed_forward(h)): one norm, both sublayers read its output.  A layer may
+    have no feed-forward.  With a "token_side" part, that part follows on the updated x (and does the addition of
+    the sublayers' contributions itself, in the same pass).
+
+    The block reads the parts "norm", "mixer" and, where the layer has them, "feed_forward" and "token_side".
+    """
+
+    def __init__(self, rt: Runtime, prefix: str, layer: LayerSpec, norm_name: str = "norm", mixer_name: str = "mixer",
+                 feed_forward_name: str = "feed_forward", token_side_name: str = "token_side"):
+        super().__init__(rt, prefix)
+        missing = [n for n in ("norm", "mixer") if n not in layer.parts]
+        if missing:
+            raise ValueError(f"layer {prefix!r}: a parallel_residual block needs the parts {', '.join(missing)}")
+        self.norm = build_part("norm", layer.parts["norm"], rt, self.name(norm_name))
+        self.mixer = build_part("mixer", layer.parts["mixer"], rt, self.name(mixer_name))
+        self.ffn = (build_part("feed_forward", layer.parts["feed_forward"], rt, self.name(feed_forward_name))
+                    if "feed_forward" in layer.parts else None)
+        self.side = (build_part("token_side", layer.parts["token_side"], rt, self.name(token_side_name))
+                     if "token_side" in layer.parts else None)
+        self.parts = tuple(p for p in (self.norm, self.mixer, self.ffn, self.side) if p is not None)
+        self.capture_safe = all(p.capture_safe and hasattr(p, "emit") for p in self.parts)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        out: Dict[str, WeightSpec] = {}
+        for p in self.parts:
+            out.update(p.weight_specs())
+        return out
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts:
+            p.load_weights({n: tensors[n] for n in p.weight_specs()})
+
+    def tied_tensors(self) -> Dict[str, str]:
+        out: Dict[str, str] = {}
+        for p in self.parts:
+            out.update(p.tied_tensors())
+        return out
+
+    def receive_tied(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts:
+            own = p.tied_tensors()
+            if own:
+                p.receive_tied({n: tensors[n] for n in own})
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def emit(self, plan: Plan, x: torch.Tensor, delta: Optional[torch.Tensor], cache):
+        hidden = x.shape[1]
+        h = emit_norm(plan, self.norm, x, delta=delta)
+        a = emit_mixer(plan, self.mixer, h, cache, hidden)
+        b = emit_feed_forward(plan, self.ffn, h, hidden) if self.ffn is not None else None
+        if self.side is not None:
+            self.side.emit(plan, x, a, b)
+            return x, None
+        if b is None:
+            return x, a                       # the next norm adds it
+        plan.residual_add(x, a, b)
+        return x, None
+
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], batch, cache):
+        plan = Plan()
+        x, out = self.emit(plan, x, delta, cache)
+        run_alone(self.rt, plan, batch)
+        return x, None if out is None else out[: x.shape[0]]

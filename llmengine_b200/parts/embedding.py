@@ -11,21 +11,35 @@ from .base import Part, Runtime, WeightSpec, register_part, run_alone
 
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
-    """x[t,:] = E[ids[t],:] as 32-bit, no scaling (src/runtime/kernels/cpu_kernels.cpp:262-274)."""
+    """x[t,:] = E[ids[t],:] as 32-bit, no scaling (src/runtime/kernels/cpu_kernels.cpp:262-274).
 
-    def __init__(self, rt: Runtime, prefix: str, vocab_size: int, hidden_size: int):
+    `leaf` is the table's name below the prefix ("" = the prefix itself).  `extra_tables` (full tensor name ->
+    width) are further per-token tables [vocab, width] that the part only stores: other parts of the model take
+    them as shared tensors and gather from them by the step's token ids."""
+
+    def __init__(self, rt: Runtime, prefix: str, vocab_size: int, hidden_size: int, leaf: str = "weight",
+                 extra_tables: Optional[Dict[str, int]] = None):
         super().__init__(rt, prefix)
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
+        self.leaf = leaf
+        self.extra_widths = {n: int(w) for n, w in dict(extra_tables or {}).items()}
         self.table: Optional[torch.Tensor] = None
+        self.extra: Dict[str, torch.Tensor] = {}
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {self.name("weight"): WeightSpec((self.vocab, self.hidden))}
+        s = {self.name(self.leaf): WeightSpec((self.vocab, self.hidden))}
+        for n, w in self.extra_widths.items():
+            s[n] = WeightSpec((self.vocab, w), init="unit")
+        return s
 
     def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
-        self.table = t[self.name("weight")].contiguous()
+        self.table = t[self.name(self.leaf)].contiguous()
+        self.extra = {n: t[n].contiguous() for n in self.extra_widths}
 
     def shared_tensor(self, name: str) -> Optional[torch.Tensor]:
-        return self.table if name == self.name("weight") else None
+        if name in self.extra:
+            return self.extra[name]
+        return self.table if name == self.name(self.leaf) else None
 
     def emit(self, plan: Plan) -> torch.Tensor:
         x = self.rt.workspace("residual", self.hidden, torch.float32)
@@ -47,25 +61,26 @@ class LMHead(Part):
     (src/io/gguf_weight_loader.cpp:46-50)."""
 
     def __init__(self, rt: Runtime, prefix: str, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None,
-                 tied: bool = False):
+                 tied: bool = False, leaf: str = "weight"):
         super().__init__(rt, prefix)
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
+        self.leaf = leaf
         self.tied_to = tied_to
         self.tied = bool(tied) or tied_to is not None
         self.weight: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {} if self.tied else {self.name("weight"): WeightSpec((self.vocab, self.hidden))}
+        return {} if self.tied else {self.name(self.leaf): WeightSpec((self.vocab, self.hidden))}
 
     def tied_tensors(self) -> Dict[str, str]:
-        return {self.name("weight"): self.tied_to} if self.tied_to is not None else {}
+        return {self.name(self.leaf): self.tied_to} if self.tied_to is not None else {}
 
     def receive_tied(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.tie(tensors[self.name("weight")])
+        self.tie(tensors[self.name(self.leaf)])
 
     def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
         if not self.tied:
-            self.weight = t[self.name("weight")].contiguous()
+            self.weight = t[self.name(self.leaf)].contiguous()
 
     def tie(self, table: torch.Tensor) -> None:
         if tuple(table.shape) != (self.vocab, self.hidden):

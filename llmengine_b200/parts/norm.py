@@ -16,17 +16,18 @@ class RMSNorm(Part):
     separate Add node before the norm (src/model/transformer_graph_builder.cpp:251-257); here
     the norm kernel takes the not-yet-added contribution `delta` and does both."""
 
-    def __init__(self, rt: Runtime, prefix: str, size: int, eps: float):
+    def __init__(self, rt: Runtime, prefix: str, size: int, eps: float, leaf: str = "weight"):
         super().__init__(rt, prefix)
         self.size = int(size)
         self.eps = float(eps)
+        self.leaf = leaf
         self.gain: Optional[torch.Tensor] = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
-        return {self.name("weight"): WeightSpec((self.size,), role="vector", init="gain")}
+        return {self.name(self.leaf): WeightSpec((self.size,), role="vector", init="gain")}
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.gain = tensors[self.name("weight")]
+        self.gain = tensors[self.name(self.leaf)]
 
     def emit(self, plan: Plan, x: torch.Tensor, delta: Optional[torch.Tensor] = None, rows: str = ROWS_TOKENS) -> torch.Tensor:
         out = self.rt.workspace("normed" if rows == ROWS_TOKENS else "normed_rows", self.size, self.rt.dtype)
@@ -40,3 +41,16 @@ class RMSNorm(Part):
         out = self.emit(plan, x, delta=delta, rows=ROWS_TOKENS if out_rows is None else ROWS_LOGITS)
         run_alone(self.rt, plan, StepBatch.bare(x.shape[0], x.device, logit_rows=out_rows))
         return out[: x.shape[0] if out_rows is None else out_rows.numel()]
+
+
+@register_part("norm", "rmsnorm_scalar")
+class ScalarGainRMSNorm(RMSNorm):
+    """y = x / sqrt(mean(x^2) + eps) * g with ONE learned number g for all coordinates (a tensor without
+    dimensions).  The kernels are those of the norm with a gain vector: the number is spread over a vector when
+    the weights are loaded, so the fused residual add and the row gather of the final norm serve it too."""
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.name(self.leaf): WeightSpec((), role="vector", init="gain")}
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.gain = tensors[self.name(self.leaf)].reshape(1).expand(self.size).contiguous()

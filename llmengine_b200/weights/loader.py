@@ -118,6 +118,9 @@ def counter_normal(key: int, start: int, count: int, device: torch.device) -> to
     return (total - 393210).to(torch.float32) * (1.0 / 65536.0)
 
 
+INIT = {"normal": (0.02, 0.0), "gain": (0.1, 1.0), "unit": (1.0, 0.0)}      # init kind -> (scale, offset) of a variate
+
+
 def random_tensor(name: str, spec: WeightSpec, seed: int, device: torch.device = torch.device("cpu")) -> torch.Tensor:
     """A 32-bit tensor drawn from (seed, name, element index) alone, so that its values depend neither on the
     order of generation nor on the device that makes them: "normal" ~ N(0, 0.02), "gain" ~ 1 + N(0, 0.1)."""
@@ -131,11 +134,10 @@ def random_tensor(name: str, spec: WeightSpec, seed: int, device: torch.device =
         n = min(step, numel - a)
         out[a:a + n] = counter_normal(key, a, n, device)
     out = out.view(tuple(spec.shape))
-    if spec.init == "gain":
-        return 1.0 + 0.1 * out
-    if spec.init == "normal":
-        return 0.02 * out
-    raise ValueError(f"tensor {name!r}: unknown init {spec.init!r}")
+    if spec.init not in INIT:
+        raise ValueError(f"tensor {name!r}: unknown init {spec.init!r}")
+    scale, offset = INIT[spec.init]
+    return offset + scale * out if offset else scale * out
 
 
 def random_model_weights(model, seed: int, compute: torch.dtype, device: torch.device,
@@ -148,9 +150,9 @@ def random_model_weights(model, seed: int, compute: torch.dtype, device: torch.d
     tensors = {}
     for name, spec in model.weight_specs().items():
         stored = stored_dtype(spec, file_dtype, compute)
-        if fill is not None and stored in (torch.float32, torch.bfloat16) and spec.init in ("normal", "gain"):
+        if fill is not None and stored in (torch.float32, torch.bfloat16) and spec.init in INIT:
             t = torch.empty(tuple(spec.shape), dtype=stored, device=device)
-            scale, offset = (0.02, 0.0) if spec.init == "normal" else (0.1, 1.0)
+            scale, offset = INIT[spec.init]
             tensors[name] = fill(t, _tensor_seed(seed, name), 0, scale, offset,
                                  round_bf16_first=file_dtype == torch.bfloat16 and stored != torch.bfloat16)
         else:

@@ -107,6 +107,64 @@ class HostOps:
         out.copy_((x.float() @ w.float().t()).to(out.dtype))
         return out
 
+    def activation(self, act, params, x, out):
+        assert act == "xielu"
+        z = x.float()
+        ap, an = params
+        out.copy_(torch.where(z > 0, ap * z * z + 0.5 * z, an * (torch.expm1(torch.clamp(z, max=0)) - z) + 0.5 * z).to(out.dtype))
+
+    def pointwise(self, kind, a, b, out):
+        assert kind == "sigmoid_mul"
+        out.copy_((a.float() * torch.sigmoid(b.float())).to(out.dtype))
+
+    def batched_linear(self, x, w, out):
+        out.copy_(torch.einsum("tbk,bnk->tbn", x.float(), w.float()).to(out.dtype))
+
+    @staticmethod
+    def _rotate(x, positions, inv_freq, dims):
+        half = dims // 2
+        ang = positions.float()[:, None] * inv_freq.float()[None, :]
+        shape = [x.shape[0]] + [1] * (x.dim() - 2) + [half]
+        c, s = torch.cos(ang).reshape(shape), torch.sin(ang).reshape(shape)
+        u, v = x[..., :half], x[..., half:dims]
+        return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], -1)
+
+    def latent_attention(self, a, T, positions, token_request, block_tables, slot_mapping, page_size):
+        H, r, dr = a["num_heads"], a["kv_rank"], a["rot_dim"]
+        cache, q, out = a["cache"], a["q"][:T].view(T, H, r + dr), a["out"][:T].view(T, H, r)
+        kv = a["kv_in"][:T].float()
+        c = kv[:, :r]
+        c = c * (1.0 / torch.sqrt((c * c).mean(-1, keepdim=True) + a["eps"])) * a["c_gain"].float()
+        row = c
+        if dr:
+            row = torch.cat([c, self._rotate(kv[:, r:], positions, a["inv_freq"], a["rot_dims"])], -1)
+            q[:, :, r:] = self._rotate(a["q_rot"][:T].float(), positions, a["inv_freq"], a["rot_dims"]).to(q.dtype)
+        flat = cache.view(-1, r + dr)
+        for t in range(T):
+            if int(slot_mapping[t]) >= 0:
+                flat[int(slot_mapping[t])] = row[t].to(cache.dtype)
+        for t in range(T):
+            p = int(positions[t])
+            bt = block_tables[int(token_request[t])]
+            js = torch.arange(0, p + 1)
+            pages = bt[(js // page_size).long()].long()
+            assert (pages >= 0).all(), "attention would read a page that is not held"
+            rows = flat[pages * page_size + (js % page_size)].float()            # [n, r + dr]
+            s = (q[t].float() @ rows.t()) * a["scale"]                           # [H, n]
+            if a["sink"] is not None:
+                s = torch.cat([s, a["sink"].float()[:, None]], -1)
+            w = torch.softmax(s, -1)[:, : p + 1]
+            out[t] = (w @ rows[:, :r]).to(out.dtype)
+
+    def token_side(self, a, T, token_ids):
+        x = a["x"][:T]
+        x += a["a"][:T].float() + (a["b"][:T].float() if a["b"] is not None else 0.0)
+        e = a["table"][token_ids.long()][:, a["offset"]:a["offset"] + a["dim"]].float()
+        z = x @ a["w_gate"].float().t()
+        g = 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3))) * e
+        y = g @ a["w_proj"].float().t()
+        x += y * (1.0 / torch.sqrt((y * y).mean(-1, keepdim=True) + a["eps"])) * a["gain"].float()
+
     def repetition_penalty(self, logits, rows, tokens, counts, penalty):
         for r, t, c in zip(rows.tolist(), tokens.tolist(), counts.tolist()):
             p = float(penalty[r])
@@ -165,6 +223,20 @@ class HostPlan:
                                     v_in=qkv[:, qs + kvs:] if w else None, q_out=a["q"], k_out=None,
                                     cache=a["cache"] if w else None), batch, T)
                 self._attend(a, batch, T)
+            elif k == "linear_act":
+                o.linear(a["x"][:T], a["w"], a["mid"][:T])
+                o.activation(a["act"], a["params"], a["mid"][:T], a["out"][:T])
+            elif k == "pointwise":
+                o.pointwise(a["what"], a["a"][:T], cut(a["b"]), a["out"][:T])
+            elif k == "batched_linear":
+                o.batched_linear(a["x"][:T], a["w"], a["out"][:T])
+            elif k == "residual_add":
+                a["x"][:T] += a["a"][:T].float() + (a["b"][:T].float() if a["b"] is not None else 0.0)
+            elif k == "latent_attention":
+                g = batch.groups[a["group"]]
+                o.latent_attention(a, T, batch.positions, batch.token_request, g.block_tables, g.slot_mapping, g.page_size)
+            elif k == "token_side":
+                o.token_side(a, T, batch.token_ids)
             elif k == "call":
                 a["fn"](batch)
             else:
