@@ -47,6 +47,8 @@ typedef int (*GeluGatherMulFn)(const void*, long long, int, const int*, const vo
 typedef int (*RmsNormAddFn)(float*, const float*, const void*, int, int, int, float, cudaStream_t);
 typedef int (*LatentPostFn)(const LlmeLatentPostArgs*, int, cudaStream_t);
 typedef int (*LatentAttnPlainFn)(const LlmeLatentAttnArgs*, int, cudaStream_t);
+typedef int (*LatentAttnTcFn)(const LlmeFastAttnArgs*, const float*, int, int, cudaStream_t);
+typedef int (*LatentFitsFn)(int);
 typedef int (*GemmF32BatchedFn)(const float*, const void*, int, float*, int, int, int, long long, long long, long long, int, long long,
                                 long long, long long, cudaStream_t);
 
@@ -496,6 +498,17 @@ int op_residual_add(LlmeExecutor& ex, const LlmeResidualAddOp& o, const LlmeStep
     return ex.launched(f(o.x, o.a, o.b, o.dtype, nullptr, 0, s.num_tokens, o.size, st), "residual_add");
 }
 
+// Key ranges per request for single tokens over a latent cache: as many blocks as the GPU has SMs, no range shorter
+// than four key tiles, at most 32.  A request's heads are one tile of rows (two from 65 heads on).
+int latent_splits(const LlmeExecutor& ex, int requests, int nh, long long max_ctx) {
+    const long long row_tiles = nh <= 64 ? 1 : (nh + 63) / 64, bn = nh <= 32 ? 64 : 32;
+    const long long tiles = (max_ctx + bn - 1) / bn;
+    long long s = ex.sms / (requests * row_tiles);
+    if (s > tiles / 4) s = tiles / 4;
+    if (s > 32) s = 32;
+    return s < 1 ? 1 : (int)s;
+}
+
 int op_latent_attention(LlmeExecutor& ex, const LlmeLatentAttentionOp& o, const LlmeStep& s, cudaStream_t st) {
     if (s.num_tokens <= 0) return 0;
     if (o.group < 0 || o.group >= s.num_groups) return ex.fail("latent attention: the step has no cache group %d", o.group);
@@ -508,6 +521,28 @@ int op_latent_attention(LlmeExecutor& ex, const LlmeLatentAttentionOp& o, const 
     p.positions = s.positions; p.q = o.q; p.cache = o.cache; p.slot_mapping = g.slot_mapping;
     p.tokens = s.num_tokens; p.nh = o.nh; p.rank = o.rank; p.rot = o.rot;
     if (int rc = ex.launched(post(&p, o.dtype, st), "latent_post")) return rc;
+    // bfloat16 with a latent size the tensor-core kernel is built for: prompt portions in one launch, single tokens in
+    // another whose requests may be cut into several key ranges
+    auto* tc = (LatentAttnTcFn)ex.find_hd("latent_attention_tc", o.rank);
+    auto* fits = (LatentFitsFn)ex.find_hd("latent_attention_tc_fits", o.rank);
+    if (tc && fits && o.dtype == LLME_DT_BF16 && ex.choice("attention") == "fast" && fits(o.rot)) {
+        LlmeFastAttnArgs f = {};
+        f.q = o.q; f.cache = o.cache; f.out = o.out; f.cu_q_lens = s.cu_q_lens; f.ctx_lens = s.ctx_lens; f.table_rows = s.state_slots;
+        f.block_tables = g.block_tables; f.scratch = o.scratch; f.max_blocks = g.max_blocks; f.nh = o.nh; f.nkv = 1;
+        f.page_size = g.page_size; f.scale = o.scale;
+        if (s.num_portion > 0) {
+            f.rows = s.portion_rows; f.n_rows = s.num_portion; f.splits = 1;
+            if (int rc = ex.launched(tc(&f, o.sink, o.rot, s.max_portion_len, st), "latent_attention_tc")) return rc;
+        }
+        if (s.num_decode > 0) {
+            f.rows = s.decode_rows; f.n_rows = s.num_decode;
+            f.splits = latent_splits(ex, s.num_decode, o.nh, s.max_decode_ctx);
+            if (f.splits > 1 && (!o.scratch || (long long)s.num_decode * f.splits * o.nh * (o.rank + 2) > o.scratch_floats)) f.splits = 1;
+            if (int rc = ex.launched(tc(&f, o.sink, o.rot, 1, st), "latent_attention_tc")) return rc;
+            if (f.splits > 1) ++ex.launches;
+        }
+        return 0;
+    }
     auto* plain = (LatentAttnPlainFn)ex.find("latent_attention_plain");
     if (!plain) return ex.fail("no latent attention kernel is registered");
     LlmeLatentAttnArgs a = {o.q, o.cache, o.out, o.sink, s.positions, s.token_request, g.block_tables, g.max_blocks, s.num_tokens,
@@ -628,6 +663,11 @@ LLME_EXPORT long long llme_attention_scratch_floats(LlmeExecutor* ex, int max_re
         if (need > most) most = need;
     }
     return most;
+}
+
+LLME_EXPORT long long llme_latent_scratch_floats(LlmeExecutor* ex, int nh, int rank) {
+    // requests x splits never exceeds the number of SMs (latent_splits)
+    return nh <= 0 || rank <= 0 ? 0 : (long long)ex->sms * nh * (rank + 2);
 }
 
 LLME_EXPORT LlmePlan* llme_plan_create(LlmeExecutor* ex) {

@@ -196,7 +196,7 @@ void llme_executor_destroy(LlmeExecutor*);
  * "gemm_skinny", "gemm_skinny_swiglu", "gemm_tc", "gemm_tc_swiglu", "attention_plain", and per head size
  * "attention_portion/<hd>", "attention_decode/<hd>", "attention_decode_fused/<hd>", "attention_tc/<hd>"; "xielu",
  * "sigmoid_mul", "residual_add", "gelu_gather_mul", "rmsnorm_add", "latent_post", "gemm_f32_batched",
- * "latent_attention_plain". */
+ * "latent_attention_plain", and per latent size "latent_attention_tc/<rank>", "latent_attention_tc_fits/<rank>". */
 int llme_executor_register(LlmeExecutor*, const char* name, void* entry_point);
 /* Which implementation an operation takes.  Operations and their variants:
  *   "linear":            "auto" | "tcgen05" | "cublas" | "plain"   (bfloat16 products of 128 tokens or more / all)
@@ -212,6 +212,8 @@ const char* llme_executor_error(LlmeExecutor*);
 long long llme_executor_launches(LlmeExecutor*);      /* kernels of this package launched so far */
 /* Scratch floats an attention record needs for steps of up to `max_requests` single tokens. */
 long long llme_attention_scratch_floats(LlmeExecutor*, int max_requests, int nh, int nkv, int hd);
+/* Scratch floats a latent attention record needs for any step of single tokens. */
+long long llme_latent_scratch_floats(LlmeExecutor*, int nh, int rank);
 /* Blocks per (request, key/value head) that the decode attention would use. */
 int llme_decode_splits(LlmeExecutor*, int requests, int nh, int nkv, int hd, int window, int max_ctx);
 

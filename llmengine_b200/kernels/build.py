@@ -30,6 +30,8 @@ SOURCES: Dict[str, str] = {
     "pointwise": "pointwise.cu",
     # attention over a cache of latent rows shared by all heads
     "attention_latent": "attention_latent.cu",
+    # the same on the tensor cores, per latent size (a multiple of 64): "attention_latent_tc@RANK=512"
+    "attention_latent_tc": "attention_latent_tc.cu",
     "gemm_f32": "gemm_f32.cu",
     "sampling": "sampling.cu",
     "gemm_skinny": "gemm_skinny.cu",
@@ -55,6 +57,7 @@ VARIANTS: Dict[str, List[str]] = {
     "attention_fast": ["attention_fast@HEAD_DIM=64", "attention_fast@HEAD_DIM=128"],
     "attention_decode_static": ["attention_decode_static@HEAD_DIM=128"],
     "attention_tc": ["attention_tc@HEAD_DIM=64", "attention_tc@HEAD_DIM=128"],
+    "attention_latent_tc": ["attention_latent_tc@RANK=128", "attention_latent_tc@RANK=512"],
 }
 
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")

@@ -170,6 +170,18 @@ class CudaOps:
     def attention_scratch_floats(self, max_requests: int, num_heads: int, num_kv_heads: int, head_dim: int) -> int:
         return int(self._xlib.llme_attention_scratch_floats(self._ex, max_requests, num_heads, num_kv_heads, head_dim))
 
+    def latent_scratch_floats(self, num_heads: int, kv_rank: int) -> int:
+        return int(self._xlib.llme_latent_scratch_floats(self._ex, num_heads, kv_rank))
+
+    @staticmethod
+    def latent_tc_supports(kv_rank: int, rot_dim: int, dtype: torch.dtype) -> bool:
+        """Whether the tensor-core latent attention is built for this shape (bfloat16, a latent size that is a
+        multiple of 64, rows of whole 16-byte pieces that fit shared memory)."""
+        if not (dtype == torch.bfloat16 and kv_rank % 64 == 0 and 64 <= kv_rank <= 1024 and rot_dim % 8 == 0):
+            return False
+        ld = ((kv_rank + rot_dim + 15) // 16) * 16 + 8
+        return (32 + 128) * ld * 2 + 32 * 72 * 2 + 4096 <= 227 * 1024
+
     def decode_splits(self, requests: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, max_ctx: int) -> int:
         return int(self._xlib.llme_decode_splits(self._ex, requests, num_heads, num_kv_heads, head_dim, window, max_ctx))
 
@@ -181,6 +193,8 @@ class CudaOps:
                       "gelu_gather_mul": "llme_gelu_gather_mul", "rmsnorm_add": "llme_rmsnorm_add",
                       "latent_post": "llme_latent_post"},
         "attention_latent": {"latent_attention_plain": "llme_latent_attention_plain"},
+        "attention_latent_tc": {"latent_attention_tc/{hd}": "llme_latent_attention_tc",
+                                "latent_attention_tc_fits/{hd}": "llme_latent_attention_tc_fits"},
         "gemm_skinny": {"gemm_skinny": "llme_gemm_skinny_bf16", "gemm_skinny_swiglu": "llme_gemm_skinny_swiglu_bf16"},
         "gemm_tcgen05": {"gemm_tc": "llme_gemm_tc_bf16", "gemm_tc_swiglu": "llme_gemm_tc_swiglu_bf16"},
         "attention_plain": {"attention_plain": "llme_attention_plain"},
@@ -218,6 +232,8 @@ class CudaOps:
                 want("pointwise")
             if op.kind == "latent_attention":
                 want("attention_latent")
+                if fast_attention and self.latent_tc_supports(a["kv_rank"], a["rot_dim"], a["q"].dtype):
+                    want(f"attention_latent_tc@RANK={a['kv_rank']}")
             if op.kind == "batched_linear" and a["x"].dtype == torch.float32:
                 want("gemm_f32")
             if op.kind == "token_side":

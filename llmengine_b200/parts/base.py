@@ -186,6 +186,16 @@ class Runtime:
             return None
         return self.buffer("attention_scratch", 1, n, torch.float32, exact=True, zero=True).view(-1)
 
+    def latent_scratch(self, num_heads: int, kv_rank: int) -> Optional[torch.Tensor]:
+        """Scratch memory of the latent attention whose requests are cut into several key ranges (one buffer for all
+        layers, as large as the widest of them needs)."""
+        need = getattr(self.ops, "latent_scratch_floats", None)
+        n = need(num_heads, kv_rank) if need is not None else 0
+        if n <= 0:
+            return None
+        self._latent_scratch_floats = max(getattr(self, "_latent_scratch_floats", 0), n)
+        return self.buffer("latent_scratch", 1, self._latent_scratch_floats, torch.float32, exact=True).view(-1)
+
     def rows(self, t: Optional[torch.Tensor], n: Optional[int] = None) -> Optional[torch.Tensor]:
         """The first rows of a workspace buffer: those of the running step's tokens (or `n` of them)."""
         if t is None:

@@ -152,7 +152,7 @@ class LatentAttention(Part):
                               inv_freq=self.position.frequencies() if self.position is not None else None,
                               rot_dims=self.position.dims if self.position is not None else 0, q=q, out=out,
                               cache=cache.kv, group=cache.group, num_heads=H, kv_rank=r, rot_dim=dr, scale=self.scale,
-                              sink=self.sink, scratch=None)
+                              sink=self.sink, scratch=rt.latent_scratch(H, r))
         heads = rt.workspace("latent_heads", self.o_size, rt.dtype)
         plan.batched_linear(out.view(T, H, r), self.w_uv, heads.view(T, H, dv))
         if self.has_gate:
