@@ -508,6 +508,10 @@ def main() -> int:
     ap.add_argument("--breakdown", action="store_true",
                     help="instead of the bench line, print the time of every operation of a layer (decode at --batch "
                          "inside a CUDA graph, and a 2,048-token prefill), timed with CUDA events")
+    ap.add_argument("--design", default=None, choices=["bepuzen"],
+                    help="instead of the bench line: this design beside the grouped-query model of equal size (prefill and "
+                         "decode tokens/s, and every record of a layer against its roofline)")
+    ap.add_argument("--size", default=None, help="with --design: one of its sizes alone (2048, 4096)")
     args = ap.parse_args()
     PAGE_SIZE = args.page_size
     if args.impl == "reference":
@@ -521,6 +525,9 @@ def main() -> int:
         from llmengine_b200.breakdown import breakdown
         return breakdown(args, SHAPES[args.shape or "8b"], CACHED, CONTEXT, PREFILL_TOKENS, peaks())
     pk = peaks()
+    if args.design:
+        from llmengine_b200.design_bench import run as run_design
+        return run_design(args, pk)
 
     # ---- one shape and mode alone
     if args.shape or args.mode:

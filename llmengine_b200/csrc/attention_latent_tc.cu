@@ -40,6 +40,9 @@ __device__ __forceinline__ void ldmatrix_x2(uint32_t addr, uint32_t& r0, uint32_
 __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t addr, uint32_t& r0, uint32_t& r1) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
 }
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
 __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -61,13 +64,13 @@ struct Args {
 
 // RG groups of 16 query rows, WG = 8 / RG warps per group, key tiles of BN.
 template <int RG, int BN>
-__global__ void __launch_bounds__(WARPS * 32) latent_attention_tc_kernel(Args a) {
+__global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_tc_kernel(Args a) {
     constexpr int WG = WARPS / RG, BM = 16 * RG;
     constexpr int KW = BN / WG, NT_S = KW / 8;             // keys and 8-key tiles of a warp's share of the scores
     constexpr int CW = RANK / WG, NT_O = CW / 8;           // columns and 8-column tiles of a warp's share of the outputs
     static_assert(KW % 8 == 0 && CW % 8 == 0, "a warp's share must be whole tiles");
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int width = RANK + a.rot, widthp = (width + 15) & ~15, ld = widthp + 8;
+    const int width = RANK + a.rot, widthp = (width + 63) & ~63, ld = widthp + 8;      // whole groups of four 16-wide steps
     __nv_bfloat16* q_s = (__nv_bfloat16*)smem_raw;                       // [BM][ld]
     __nv_bfloat16* k_s = q_s + (size_t)BM * ld;                          // [2][BN][ld]
     __nv_bfloat16* p_s = k_s + (size_t)2 * BN * ld;                      // [BM][BN + 8]
@@ -86,8 +89,8 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_tc_kernel(Args a)
     const int last_row = min(row0 + BM, n_rows) - 1;
     const int pmax = first_pos + last_row / H;                           // the farthest key any row of the tile sees
     const int tiles = pmax / BN + 1;
-    const int per = (tiles + a.splits - 1) / a.splits;
-    const int t_begin = split * per, t_end = min(tiles, t_begin + per);
+    // the tiles are dealt out evenly: with more ranges than tiles the later ranges get one tile each or none
+    const int t_begin = (int)((long long)split * tiles / a.splits), t_end = (int)((long long)(split + 1) * tiles / a.splits);
     const int* bt = a.block_tables + (size_t)a.table_rows[r] * a.max_blocks;
     const int ps = a.page_size;
     const int chunks = width >> 3;                                       // 16-byte pieces of a row
@@ -102,18 +105,20 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_tc_kernel(Args a)
     }
     pdl_wait();
 
+    // A warp brings whole key rows: one block-table lookup per row (every lane reads the same entry), the lanes share
+    // the row's 16-byte pieces.
     auto load_keys = [&](int tile, int stage) {
         __nv_bfloat16* dst = k_s + (size_t)stage * BN * ld;
         const int j0 = tile * BN;
-        for (int e = tid; e < BN * chunks; e += blockDim.x) {
-            const int kr = e / chunks, c = e - kr * chunks;
+        for (int kr = warp; kr < BN; kr += WARPS) {
             const int j = j0 + kr;
-            __nv_bfloat16* d = dst + (size_t)kr * ld + c * 8;
+            __nv_bfloat16* d = dst + (size_t)kr * ld;
             if (j <= pmax) {
-                const int page = bt[j / ps];
-                cp_async16(d, a.cache + ((size_t)page * ps + (j - (j / ps) * ps)) * width + c * 8);
+                const int blk = j / ps;
+                const __nv_bfloat16* src = a.cache + ((size_t)bt[blk] * ps + (j - blk * ps)) * width;
+                for (int c = lane; c < chunks; c += 32) cp_async16(d + c * 8, src + c * 8);
             } else {
-                *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+                for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
             }
         }
     };
@@ -121,11 +126,13 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_tc_kernel(Args a)
     // Q tile: rows (token, head) of one request are contiguous in memory
     {
         const __nv_bfloat16* src = a.q + ((size_t)tok0 * H + row0) * width;
-        for (int e = tid; e < BM * chunks; e += blockDim.x) {
-            const int qr = e / chunks, c = e - qr * chunks;
-            __nv_bfloat16* d = q_s + (size_t)qr * ld + c * 8;
-            if (row0 + qr < n_rows) cp_async16(d, src + (size_t)qr * width + c * 8);
-            else *reinterpret_cast<uint4*>(d) = make_uint4(0u, 0u, 0u, 0u);
+        for (int qr = warp; qr < BM; qr += WARPS) {
+            __nv_bfloat16* d = q_s + (size_t)qr * ld;
+            if (row0 + qr < n_rows) {
+                for (int c = lane; c < chunks; c += 32) cp_async16(d + c * 8, src + (size_t)qr * width + c * 8);
+            } else {
+                for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(d + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
         }
     }
     if (t_begin < t_end) load_keys(t_begin, 0);
@@ -158,17 +165,45 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_tc_kernel(Args a)
         float s[NT_S][4];
 #pragma unroll
         for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+        // Four steps of 16 along the row at a time: their fragments are all requested before the first product, so the
+        // shared-memory latency of one step hides behind the products of the others (a block is one per SM, eight warps).
         const uint32_t q_addr = smem_u32(q_s + (size_t)(rg * 16 + (lane & 15)) * ld + (lane >> 4) * 8);
-        const uint32_t k_addr = smem_u32(kt + (size_t)(wg * KW + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
-        for (int ks = 0; ks < widthp / 16; ++ks) {
-            uint32_t a0, a1, a2, a3;
-            ldmatrix_x4(q_addr + ks * 32, a0, a1, a2, a3);
+        if constexpr (NT_S % 2 == 0) {
+            // key fragments of two 8-key tiles per load: matrices (keys 0-7 | 8-15) x (columns 0-7 | 8-15)
+            const uint32_t k_addr = smem_u32(kt + (size_t)(wg * KW + (lane & 7) + ((lane >> 4) << 3)) * ld + ((lane >> 3) & 1) * 8);
+            for (int ks = 0; ks < widthp / 16; ks += 4) {
+                uint32_t qa[4][4], kb[4][NT_S / 2][4];
 #pragma unroll
-            for (int nt = 0; nt < NT_S; ++nt) {
-                uint32_t b0, b1;
-                ldmatrix_x2(k_addr + (uint32_t)(nt * 8 * ld * 2) + ks * 32, b0, b1);
-                mma_bf16(s[nt], a0, a1, a2, a3, b0, b1);
+                for (int u = 0; u < 4; ++u) {
+                    ldmatrix_x4(q_addr + (ks + u) * 32, qa[u][0], qa[u][1], qa[u][2], qa[u][3]);
+#pragma unroll
+                    for (int np = 0; np < NT_S / 2; ++np)
+                        ldmatrix_x4(k_addr + (uint32_t)(np * 16 * ld * 2) + (ks + u) * 32, kb[u][np][0], kb[u][np][1], kb[u][np][2], kb[u][np][3]);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int np = 0; np < NT_S / 2; ++np) {
+                        mma_bf16(s[2 * np], qa[u][0], qa[u][1], qa[u][2], qa[u][3], kb[u][np][0], kb[u][np][1]);
+                        mma_bf16(s[2 * np + 1], qa[u][0], qa[u][1], qa[u][2], qa[u][3], kb[u][np][2], kb[u][np][3]);
+                    }
             }
+        } else {
+            const uint32_t k_addr = smem_u32(kt + (size_t)(wg * KW + (lane & 7)) * ld + ((lane >> 3) & 1) * 8);
+            // one 8-key tile: two accumulators (even and odd steps) keep two products in flight, added at the end
+            float s2[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int ks = 0; ks < widthp / 16; ks += 4) {
+                uint32_t qa[4][4], kb[4][2];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    ldmatrix_x4(q_addr + (ks + u) * 32, qa[u][0], qa[u][1], qa[u][2], qa[u][3]);
+                    ldmatrix_x2(k_addr + (ks + u) * 32, kb[u][0], kb[u][1]);
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) mma_bf16((u & 1) ? s2 : s[0], qa[u][0], qa[u][1], qa[u][2], qa[u][3], kb[u][0], kb[u][1]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) s[0][i] += s2[i];
         }
         // 2. scale, mask, row maxima over the whole tile
         float t0 = -INFINITY, t1 = -INFINITY;
@@ -223,16 +258,23 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_tc_kernel(Args a)
             o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1;
         }
         const uint32_t p_addr = smem_u32(p_s + (size_t)(rg * 16 + (lane & 15)) * LDP + (lane >> 4) * 8);
-        const uint32_t v_addr = smem_u32(kt + (size_t)(lane & 15) * ld + wg * CW);
+        // value fragments of two 8-column tiles per load: matrices (keys 0-7 | 8-15) x (columns 0-7 | 8-15), transposed
+        const uint32_t v_addr = smem_u32(kt + (size_t)(lane & 15) * ld + wg * CW + (lane >> 4) * 8);
 #pragma unroll
         for (int ks = 0; ks < BN / 16; ++ks) {
             uint32_t a0, a1, a2, a3;
             ldmatrix_x4(p_addr + ks * 32, a0, a1, a2, a3);
 #pragma unroll
-            for (int nt = 0; nt < NT_O; ++nt) {
+            for (int np = 0; np < NT_O / 2; ++np) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(v_addr + (uint32_t)(ks * 16 * ld * 2) + np * 32, b0, b1, b2, b3);
+                mma_bf16(o[2 * np], a0, a1, a2, a3, b0, b1);
+                mma_bf16(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
+            }
+            if constexpr (NT_O % 2 == 1) {
                 uint32_t b0, b1;
-                ldmatrix_x2_trans(v_addr + (uint32_t)(ks * 16 * ld * 2) + nt * 16, b0, b1);
-                mma_bf16(o[nt], a0, a1, a2, a3, b0, b1);
+                ldmatrix_x2_trans(v_addr + (uint32_t)(ks * 16 * ld * 2) + (NT_O - 1) * 16, b0, b1);
+                mma_bf16(o[NT_O - 1], a0, a1, a2, a3, b0, b1);
             }
         }
     }
@@ -281,35 +323,55 @@ __global__ void __launch_bounds__(WARPS * 32) latent_attention_tc_kernel(Args a)
     }
 }
 
-// One block per (request of the list, head): adds the splits' partial sums in the order of the splits.
+// One block per (request of the list, head): the ranges' weights exp(m_s - M) / L are formed once by the first warp,
+// then every thread adds its columns over the ranges in their order (loads of different ranges are independent).
 __global__ void latent_merge_kernel(const float* __restrict__ scratch, __nv_bfloat16* __restrict__ out, const int* __restrict__ rows,
                                     const int* __restrict__ cu_q_lens, int nh, int splits) {
+    __shared__ float weight[64];
     pdl_wait();
     const int n = blockIdx.y, h = blockIdx.x;
     const int tok = cu_q_lens[rows[n]];
     const float* base = scratch + ((size_t)n * splits * nh + h) * (RANK + 2);
     const size_t step = (size_t)nh * (RANK + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, base[s * step + RANK]);
-    float L = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float m = base[s * step + RANK];
-        if (m != -INFINITY) L += base[s * step + RANK + 1] * expf(m - M);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float m[2], l[2];
+        float M = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int s = lane + 32 * i;
+            m[i] = s < splits ? base[s * step + RANK] : -INFINITY;
+            l[i] = s < splits ? base[s * step + RANK + 1] : 0.0f;
+            M = fmaxf(M, m[i]);
+        }
+        M = warp_max(M);
+        float e[2], L = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            e[i] = m[i] == -INFINITY ? 0.0f : expf(m[i] - M);
+            L += l[i] * e[i];
+        }
+        // the sum over the ranges in a fixed order
+        float total = 0.0f;
+        for (int s = 0; s < splits; ++s) total += __shfl_sync(0xffffffffu, (s < 32 ? l[0] * e[0] : l[1] * e[1]), s & 31);
+        const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+            if (lane + 32 * i < splits) weight[lane + 32 * i] = e[i] * inv;
+        (void)L;
     }
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+    __syncthreads();
     for (int c = threadIdx.x; c < RANK; c += blockDim.x) {
         float acc = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const float m = base[s * step + RANK];
-            if (m != -INFINITY) acc += base[s * step + c] * expf(m - M);
-        }
-        out[((size_t)tok * nh + h) * RANK + c] = __float2bfloat16_rn(acc * inv);
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) acc += base[s * step + c] * weight[s];
+        out[((size_t)tok * nh + h) * RANK + c] = __float2bfloat16_rn(acc);
     }
 }
 
 template <int RG, int BN>
 size_t smem_bytes(int rot) {
-    const int widthp = (RANK + rot + 15) & ~15, ld = widthp + 8, BM = 16 * RG;
+    const int widthp = (RANK + rot + 63) & ~63, ld = widthp + 8, BM = 16 * RG;
     return ((size_t)BM * ld + (size_t)2 * BN * ld + (size_t)BM * (BN + 8)) * 2 + (size_t)(WARPS / RG) * BM * 4;
 }
 
@@ -335,7 +397,7 @@ int launch(const Args& a, int n_list, int max_q_len, cudaStream_t stream) {
 // Whether rows of RANK + rot values fit the kernel (shared memory of the wider configuration).
 LLME_API int llme_latent_attention_tc_fits(int rot) {
     if (rot < 0 || (RANK + rot) % 8) return 0;
-    return smem_bytes<4, 32>(rot) <= 227u * 1024 && smem_bytes<2, 64>(rot) <= 227u * 1024 ? 1 : 0;
+    return smem_bytes<2, 64>(rot) <= 227u * 1024 ? 1 : 0;
 }
 
 // Scratch floats for `n_rows` requests of single tokens with `splits` blocks each.
@@ -352,15 +414,15 @@ LLME_API int llme_latent_attention_tc(const LlmeFastAttnArgs* f, const float* si
     if (!llme_latent_attention_tc_fits(rot)) LLME_REFUSE("latent attention: rows of %d + %d values do not fit this kernel", RANK, rot);
     const int splits = f->splits < 1 ? 1 : f->splits;
     if (splits > 1 && (max_q_len != 1 || !f->scratch)) LLME_REFUSE("latent attention: splits need single tokens and scratch memory");
-    if (f->n_rows > 65535 || splits > 65535) LLME_REFUSE("latent attention: too many requests or splits for one launch");
+    if (f->n_rows > 65535 || splits > 64) LLME_REFUSE("latent attention: too many requests or splits for one launch");
     Args a = {(const __nv_bfloat16*)f->q, (const __nv_bfloat16*)f->cache, (__nv_bfloat16*)f->out, sink, f->rows, f->cu_q_lens, f->ctx_lens,
               f->table_rows, f->block_tables, f->scratch, f->max_blocks, f->nh, rot, f->page_size, splits, f->scale};
     int rc;
     if ((long long)max_q_len * f->nh <= 16) rc = launch<1, 64>(a, f->n_rows, max_q_len, stream);
     else if ((long long)max_q_len * f->nh <= 32) rc = launch<2, 64>(a, f->n_rows, max_q_len, stream);
-    else rc = launch<4, 32>(a, f->n_rows, max_q_len, stream);
+    else rc = launch<2, 32>(a, f->n_rows, max_q_len, stream);      // two blocks fit an SM: sixteen warps hide one another's waits
     if (rc || splits == 1) return rc;
-    llme_launch(latent_merge_kernel, dim3(f->nh, f->n_rows), dim3(RANK >= 256 ? 128 : 64), 0, stream, (const float*)f->scratch,
+    llme_launch(latent_merge_kernel, dim3(f->nh, f->n_rows), dim3(RANK >= 512 ? 256 : (RANK >= 256 ? 128 : 64)), 0, stream, (const float*)f->scratch,
                 (__nv_bfloat16*)f->out, f->rows, f->cu_q_lens, f->nh, splits);
     LLME_LAUNCH_STATUS();
 }

@@ -499,12 +499,12 @@ int op_residual_add(LlmeExecutor& ex, const LlmeResidualAddOp& o, const LlmeStep
 }
 
 // Key ranges per request for single tokens over a latent cache: as many blocks as the GPU has SMs, no range shorter
-// than four key tiles, at most 32.  A request's heads are one tile of rows (two from 65 heads on).
+// than two key tiles, at most 32.  A request's heads are one tile of rows per 32 heads.
 int latent_splits(const LlmeExecutor& ex, int requests, int nh, long long max_ctx) {
-    const long long row_tiles = nh <= 64 ? 1 : (nh + 63) / 64, bn = nh <= 32 ? 64 : 32;
+    const long long row_tiles = (nh + 31) / 32, bn = nh <= 32 ? 64 : 32;
     const long long tiles = (max_ctx + bn - 1) / bn;
     long long s = ex.sms / (requests * row_tiles);
-    if (s > tiles / 4) s = tiles / 4;
+    if (s > tiles / 2) s = tiles / 2;
     if (s > 32) s = 32;
     return s < 1 ? 1 : (int)s;
 }

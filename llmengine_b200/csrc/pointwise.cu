@@ -28,16 +28,26 @@ __global__ void xielu_kernel(const T* __restrict__ in, long long ld_in, T* __res
     pdl_wait();
     const T* i = in + (size_t)blockIdx.x * ld_in;
     T* o = out + (size_t)blockIdx.x * ld_out;
-    for (int j = threadIdx.x; j < cols; j += blockDim.x) o[j] = from_f32<T>(xielu(to_f32(i[j]), a_pos, a_neg));
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x)
+        o[j] = from_f32<T>(xielu(to_f32(i[j]), a_pos, a_neg));
+}
+
+// Rows are few and wide in a decode step and many in a prompt: a second grid dimension walks the columns in pieces, as
+// many as it takes to put about four blocks on every SM, each thread then handling a handful of values.
+static dim3 grid_for(int rows, int cols, int threads) {
+    int pieces = (cols + threads - 1) / threads;
+    const int wanted = (592 + rows - 1) / rows;
+    if (pieces > wanted) pieces = wanted;
+    return dim3(rows, pieces < 1 ? 1 : pieces);
 }
 
 LLME_API int llme_xielu(const void* in, long long ld_in, void* out, long long ld_out, int dtype, int rows, int cols,
                         float a_pos, float a_neg, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (!in || !out) LLME_REFUSE("xielu: null pointer");
-    const int threads = cols >= 1024 ? 256 : 128;
-    if (dtype == LLME_F32) llme_launch(xielu_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)in, ld_in, (float*)out, ld_out, cols, a_pos, a_neg);
-    else if (dtype == LLME_BF16) llme_launch(xielu_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (const __nv_bfloat16*)in, ld_in, (__nv_bfloat16*)out, ld_out, cols, a_pos, a_neg);
+    const int threads = 128;
+    if (dtype == LLME_F32) llme_launch(xielu_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)in, ld_in, (float*)out, ld_out, cols, a_pos, a_neg);
+    else if (dtype == LLME_BF16) llme_launch(xielu_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)in, ld_in, (__nv_bfloat16*)out, ld_out, cols, a_pos, a_neg);
     else LLME_REFUSE("xielu: unsupported dtype %d", dtype);
     LLME_LAUNCH_STATUS();
 }
@@ -51,16 +61,17 @@ __global__ void sigmoid_mul_kernel(const T* __restrict__ a, long long lda, const
     const T* ar = a + (size_t)blockIdx.x * lda;
     const T* br = b + (size_t)blockIdx.x * ldb;
     T* o = out + (size_t)blockIdx.x * ldo;
-    for (int j = threadIdx.x; j < cols; j += blockDim.x) o[j] = from_f32<T>(to_f32(ar[j]) * sigmoid(to_f32(br[j])));
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x)
+        o[j] = from_f32<T>(to_f32(ar[j]) * sigmoid(to_f32(br[j])));
 }
 
 LLME_API int llme_sigmoid_mul(const void* a, long long lda, const void* b, long long ldb, void* out, long long ldo, int dtype,
                               int rows, int cols, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (!a || !b || !out) LLME_REFUSE("sigmoid_mul: null pointer");
-    const int threads = cols >= 1024 ? 256 : 128;
-    if (dtype == LLME_F32) llme_launch(sigmoid_mul_kernel<float>, dim3(rows), dim3(threads), 0, stream, (const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, cols);
-    else if (dtype == LLME_BF16) llme_launch(sigmoid_mul_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, cols);
+    const int threads = 128;
+    if (dtype == LLME_F32) llme_launch(sigmoid_mul_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)a, lda, (const float*)b, ldb, (float*)out, ldo, cols);
+    else if (dtype == LLME_BF16) llme_launch(sigmoid_mul_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)a, lda, (const __nv_bfloat16*)b, ldb, (__nv_bfloat16*)out, ldo, cols);
     else LLME_REFUSE("sigmoid_mul: unsupported dtype %d", dtype);
     LLME_LAUNCH_STATUS();
 }
@@ -71,7 +82,7 @@ __global__ void residual_add_kernel(float* __restrict__ x, const A* __restrict__
     pdl_launch_dependents();
     pdl_wait();
     const size_t base = (size_t)blockIdx.x * cols;
-    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x) {
         float v = to_f32(a[base + j]);
         if (b) v += to_f32(b[base + j]);
         v = x[base + j] + v;                 // the sublayers' contributions are summed first, then added to the stream
@@ -84,8 +95,8 @@ LLME_API int llme_residual_add(float* x, const void* a, const void* b, int ab_dt
                                cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (!x || !a) LLME_REFUSE("residual_add: null pointer");
-    const int threads = cols >= 1024 ? 256 : 128;
-#define LLME_RA(A, C) llme_launch(residual_add_kernel<A, C>, dim3(rows), dim3(threads), 0, stream, x, (const A*)a, (const A*)b, (C*)copy, cols)
+    const int threads = 128;
+#define LLME_RA(A, C) llme_launch(residual_add_kernel<A, C>, grid_for(rows, cols, threads), dim3(threads), 0, stream, x, (const A*)a, (const A*)b, (C*)copy, cols)
     if (ab_dtype == LLME_F32 && (copy_dtype == LLME_F32 || !copy)) LLME_RA(float, float);
     else if (ab_dtype == LLME_F32 && copy_dtype == LLME_BF16) LLME_RA(float, __nv_bfloat16);
     else if (ab_dtype == LLME_BF16 && (copy_dtype == LLME_BF16 || !copy)) LLME_RA(__nv_bfloat16, __nv_bfloat16);
@@ -106,7 +117,8 @@ __global__ void gelu_gather_mul_kernel(const T* __restrict__ z, long long ldz, c
     const W* e = table + (size_t)(ok ? id : 0) * ld_table + offset;
     const T* zr = z + (size_t)blockIdx.x * ldz;
     T* o = out + (size_t)blockIdx.x * ldo;
-    for (int j = threadIdx.x; j < cols; j += blockDim.x) o[j] = from_f32<T>(ok ? gelu_tanh(to_f32(zr[j])) * to_f32(e[j]) : 0.0f);
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x)
+        o[j] = from_f32<T>(ok ? gelu_tanh(to_f32(zr[j])) * to_f32(e[j]) : 0.0f);
 }
 
 LLME_API int llme_gelu_gather_mul(const void* z, long long ldz, int dtype, const int* ids, const void* table, int table_dtype,
@@ -116,8 +128,8 @@ LLME_API int llme_gelu_gather_mul(const void* z, long long ldz, int dtype, const
     if (!z || !ids || !table || !out) LLME_REFUSE("gelu_gather_mul: null pointer");
     if (table_dtype != dtype) LLME_REFUSE("gelu_gather_mul: the table is stored in the type of the activations");
     const int threads = cols >= 256 ? 256 : (cols >= 64 ? 64 : 32);
-    if (dtype == LLME_F32) llme_launch(gelu_gather_mul_kernel<float, float>, dim3(rows), dim3(threads), 0, stream, (const float*)z, ldz, ids, (const float*)table, ld_table, offset, vocab, (float*)out, ldo, cols);
-    else if (dtype == LLME_BF16) llme_launch(gelu_gather_mul_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, (const __nv_bfloat16*)z, ldz, ids, (const __nv_bfloat16*)table, ld_table, offset, vocab, (__nv_bfloat16*)out, ldo, cols);
+    if (dtype == LLME_F32) llme_launch(gelu_gather_mul_kernel<float, float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)z, ldz, ids, (const float*)table, ld_table, offset, vocab, (float*)out, ldo, cols);
+    else if (dtype == LLME_BF16) llme_launch(gelu_gather_mul_kernel<__nv_bfloat16, __nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)z, ldz, ids, (const __nv_bfloat16*)table, ld_table, offset, vocab, (__nv_bfloat16*)out, ldo, cols);
     else LLME_REFUSE("gelu_gather_mul: unsupported dtype %d", dtype);
     LLME_LAUNCH_STATUS();
 }
@@ -143,7 +155,7 @@ LLME_API int llme_rmsnorm_add(float* x, const float* y, const void* gain, int ga
                               cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (!x || !y || !gain) LLME_REFUSE("rmsnorm_add: null pointer");
-    const int threads = cols >= 1024 ? 256 : 128;
+    const int threads = cols >= 4096 ? 1024 : (cols >= 2048 ? 512 : (cols >= 1024 ? 256 : 128));
     if (gain_dtype == LLME_F32) llme_launch(rmsnorm_add_kernel<float>, dim3(rows), dim3(threads), 0, stream, x, y, (const float*)gain, cols, eps);
     else if (gain_dtype == LLME_BF16) llme_launch(rmsnorm_add_kernel<__nv_bfloat16>, dim3(rows), dim3(threads), 0, stream, x, y, (const __nv_bfloat16*)gain, cols, eps);
     else LLME_REFUSE("rmsnorm_add: unsupported gain dtype %d", gain_dtype);
@@ -174,7 +186,7 @@ __global__ void latent_post_kernel(LlmeLatentPostArgs a) {
     const int slot = a.slot_mapping ? a.slot_mapping[t] : -1;
     const int pos = a.positions[t];
     T* row = (a.cache && slot >= 0) ? (T*)a.cache + (size_t)slot * width : nullptr;
-    if (row) {                                          // uniform over the block
+    if (row && blockIdx.y == 0) {                       // uniform over the block
         float ss = 0.0f;
         for (int j = threadIdx.x; j < rank; j += blockDim.x) {
             const float v = to_f32(kv[j]);
@@ -186,10 +198,11 @@ __global__ void latent_post_kernel(LlmeLatentPostArgs a) {
         for (int j = threadIdx.x; j < rank; j += blockDim.x) row[j] = from_f32<T>((to_f32(kv[j]) * rinv) * to_f32(gain[j]));
         for (int j = threadIdx.x; j < rot; j += blockDim.x) row[rank + j] = from_f32<T>(rotated_value(kv + rank, j, a.rot_dims, a.inv_freq, pos));
     }
-    if (rot > 0 && a.q_rot && a.q) {
+    if (rot > 0 && a.q_rot && a.q && (gridDim.y == 1 || blockIdx.y > 0)) {
         const T* qr = (const T*)a.q_rot + (size_t)t * a.q_rot_stride;
         T* q = (T*)a.q + (size_t)t * a.nh * width;
-        for (int e = threadIdx.x; e < a.nh * rot; e += blockDim.x) {
+        const int first = gridDim.y == 1 ? 0 : blockIdx.y - 1, stride = gridDim.y == 1 ? 1 : gridDim.y - 1;
+        for (int e = first * blockDim.x + threadIdx.x; e < a.nh * rot; e += stride * blockDim.x) {
             const int h = e / rot, j = e - h * rot;
             q[(size_t)h * width + rank + j] = from_f32<T>(rotated_value(qr + (size_t)h * a.q_rot_head_stride, j, a.rot_dims, a.inv_freq, pos));
         }
@@ -204,7 +217,12 @@ LLME_API int llme_latent_post(const LlmeLatentPostArgs* args, int dtype, cudaStr
     if (a.rot > 0 && (!a.inv_freq || a.rot_dims <= 0 || a.rot_dims % 2 || a.rot_dims > a.rot))
         LLME_REFUSE("latent_post: %d rotated coordinates of %d need frequencies and an even count", a.rot_dims, a.rot);
     const int threads = 128;
-#define LLME_LP(T, G) llme_launch(latent_post_kernel<T, G>, dim3(a.tokens), dim3(threads), 0, stream, a)
+    // block (t, 0) norms, rotates and stores the token's cache row; blocks (t, 1..) rotate the heads' query parts
+    int q_blocks = a.rot > 0 && a.q_rot ? (a.nh * a.rot + threads - 1) / threads : 0;
+    if (q_blocks > 8) q_blocks = 8;
+    if (a.tokens > 256) q_blocks = q_blocks ? 1 : 0;
+    const dim3 grid(a.tokens, 1 + q_blocks);
+#define LLME_LP(T, G) llme_launch(latent_post_kernel<T, G>, grid, dim3(threads), 0, stream, a)
     if (dtype == LLME_F32 && a.gain_dtype == LLME_F32) LLME_LP(float, float);
     else if (dtype == LLME_BF16 && a.gain_dtype == LLME_BF16) LLME_LP(__nv_bfloat16, __nv_bfloat16);
     else if (dtype == LLME_BF16 && a.gain_dtype == LLME_F32) LLME_LP(__nv_bfloat16, float);

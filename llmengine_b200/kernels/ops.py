@@ -179,7 +179,7 @@ class CudaOps:
         multiple of 64, rows of whole 16-byte pieces that fit shared memory)."""
         if not (dtype == torch.bfloat16 and kv_rank % 64 == 0 and 64 <= kv_rank <= 1024 and rot_dim % 8 == 0):
             return False
-        ld = ((kv_rank + rot_dim + 15) // 16) * 16 + 8
+        ld = ((kv_rank + rot_dim + 63) // 64) * 64 + 8
         return (32 + 128) * ld * 2 + 32 * 72 * 2 + 4096 <= 227 * 1024
 
     def decode_splits(self, requests: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, max_ctx: int) -> int:
