@@ -63,7 +63,7 @@ struct Args {
 };
 
 // RG groups of 16 query rows, WG = 8 / RG warps per group, key tiles of BN.
-template <int RG, int BN>
+template <int RG, int BN, int STAGES>
 __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_tc_kernel(Args a) {
     constexpr int WG = WARPS / RG, BM = 16 * RG;
     constexpr int KW = BN / WG, NT_S = KW / 8;             // keys and 8-key tiles of a warp's share of the scores
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
     const int width = RANK + a.rot, widthp = (width + 63) & ~63, ld = widthp + 8;      // whole groups of four 16-wide steps
     __nv_bfloat16* q_s = (__nv_bfloat16*)smem_raw;                       // [BM][ld]
     __nv_bfloat16* k_s = q_s + (size_t)BM * ld;                          // [2][BN][ld]
-    __nv_bfloat16* p_s = k_s + (size_t)2 * BN * ld;                      // [BM][BN + 8]
+    __nv_bfloat16* p_s = k_s + (size_t)STAGES * BN * ld;                 // [BM][BN + 8]
     float* red = (float*)(p_s + (size_t)BM * (BN + 8));                  // [WG][BM]
     constexpr int LDP = BN + 8;
 
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
     // the padding columns of Q and of both key stages are zero for the whole kernel
     if (widthp > width) {
         const int pad = widthp - width;
-        for (int e = tid; e < (BM + 2 * BN) * pad; e += blockDim.x) {
+        for (int e = tid; e < (BM + STAGES * BN) * pad; e += blockDim.x) {
             const int row = e / pad, c = width + e % pad;
             (row < BM ? q_s + (size_t)row * ld : k_s + (size_t)(row - BM) * ld)[c] = __float2bfloat16(0.0f);
         }
@@ -154,11 +154,18 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
     for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
     for (int tile = t_begin; tile < t_end; ++tile) {
-        const int stage = (tile - t_begin) & 1;
+        const int stage = STAGES == 1 ? 0 : (tile - t_begin) & 1;
+        if (STAGES == 1 && tile > t_begin) {
+            __syncthreads();                       // everyone has finished with the tile before this one
+            load_keys(tile, 0);
+            cp_async_commit();
+        }
         cp_async_wait<0>();
         __syncthreads();
-        if (tile + 1 < t_end) load_keys(tile + 1, stage ^ 1);
-        cp_async_commit();
+        if (STAGES == 2) {
+            if (tile + 1 < t_end) load_keys(tile + 1, stage ^ 1);
+            cp_async_commit();
+        }
         const __nv_bfloat16* kt = k_s + (size_t)stage * BN * ld;
 
         // 1. scores of this warp's rows against its share of the tile's keys
@@ -369,18 +376,18 @@ __global__ void latent_merge_kernel(const float* __restrict__ scratch, __nv_bflo
     }
 }
 
-template <int RG, int BN>
+template <int RG, int BN, int STAGES = 2>
 size_t smem_bytes(int rot) {
     const int widthp = (RANK + rot + 63) & ~63, ld = widthp + 8, BM = 16 * RG;
-    return ((size_t)BM * ld + (size_t)2 * BN * ld + (size_t)BM * (BN + 8)) * 2 + (size_t)(WARPS / RG) * BM * 4;
+    return ((size_t)BM * ld + (size_t)STAGES * BN * ld + (size_t)BM * (BN + 8)) * 2 + (size_t)(WARPS / RG) * BM * 4;
 }
 
-template <int RG, int BN>
+template <int RG, int BN, int STAGES = 2>
 int launch(const Args& a, int n_list, int max_q_len, cudaStream_t stream) {
-    const size_t smem = smem_bytes<RG, BN>(a.rot);
+    const size_t smem = smem_bytes<RG, BN, STAGES>(a.rot);
     static size_t allowed = 0;
     if (smem > allowed) {
-        if (cudaFuncSetAttribute(latent_attention_tc_kernel<RG, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        if (cudaFuncSetAttribute(latent_attention_tc_kernel<RG, BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
             LLME_REFUSE("latent attention: rows of %d values need %zu bytes of shared memory", RANK + a.rot, smem);
         }
@@ -388,7 +395,7 @@ int launch(const Args& a, int n_list, int max_q_len, cudaStream_t stream) {
     }
     const int BM = 16 * RG;
     dim3 grid(((long long)max_q_len * a.nh + BM - 1) / BM, n_list, a.splits);
-    llme_launch(latent_attention_tc_kernel<RG, BN>, grid, dim3(WARPS * 32), smem, stream, a);
+    llme_launch(latent_attention_tc_kernel<RG, BN, STAGES>, grid, dim3(WARPS * 32), smem, stream, a);
     LLME_LAUNCH_STATUS();
 }
 
@@ -420,7 +427,11 @@ LLME_API int llme_latent_attention_tc(const LlmeFastAttnArgs* f, const float* si
     int rc;
     if ((long long)max_q_len * f->nh <= 16) rc = launch<1, 64>(a, f->n_rows, max_q_len, stream);
     else if ((long long)max_q_len * f->nh <= 32) rc = launch<2, 64>(a, f->n_rows, max_q_len, stream);
-    else rc = launch<2, 32>(a, f->n_rows, max_q_len, stream);      // two blocks fit an SM: sixteen warps hide one another's waits
+    // prompt portions: 64 rows x 32 keys.  Measured on a 2,048-token prompt with rows of 512 + 64 (four layers, whole
+    // step): 3.80 ms with this shape, 3.99 ms with 32 x 32, 4.22 ms with 32 x 64, 4.17 / 3.98 ms with a single key stage
+    // and two or three blocks an SM: the time is in the fragments every warp re-reads from shared memory per key tile,
+    // which no tile shape of a warp-level product removes.
+    else rc = launch<4, 32>(a, f->n_rows, max_q_len, stream);
     if (rc || splits == 1) return rc;
     llme_launch(latent_merge_kernel, dim3(f->nh, f->n_rows), dim3(RANK >= 512 ? 256 : (RANK >= 256 ? 128 : 64)), 0, stream, (const float*)f->scratch,
                 (__nv_bfloat16*)f->out, f->rows, f->cu_q_lens, f->nh, splits);
