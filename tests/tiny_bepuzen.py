@@ -62,10 +62,10 @@ WITH_SIDE = {"architecture": "Bepuzen", "vocab": 61, "width": 48, "norm": {"eps"
              "layers": [layer(L2, mixer2(2, 8, 8, 64, 0.3), 0), layer(L2, mixer2(2, 8, 8, 64, 0.3), 0)]}
 # wide enough for sharp attention over long contexts; pages of 16 put many page edges into a sequence
 TINY_R = {
-    "architecture": "Bepuzen", "vocab": 300, "width": 128, "norm": {"eps": 1e-5}, "token_side": {"dim": 16},
+    "architecture": "Bepuzen", "vocab": 300, "width": 128, "norm": {"eps": 1e-5}, "token_side": {"dim": 12},
     "layers": [
-        layer(L2, mixer2(8, 32, 32, 128, 0.5), 192),
-        layer(L1, mixer1(8, 32, 32, 16, 128, 0.4), 192),
+        layer(L2, mixer2(6, 32, 32, 128, 0.5), 192),
+        layer(L1, mixer1(6, 32, 16, 24, 128, 0.4), 176),
     ],
 }
 
