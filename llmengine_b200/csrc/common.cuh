@@ -91,6 +91,11 @@ inline cudaError_t llme_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
 // issues the matrix instructions.  The 32-bit path keeps expf and the division.
 __device__ __forceinline__ float silu_mul_bf16(float g, float u) { return (g * __frcp_rn(1.0f + __expf(-g))) * u; }
 
+// xIELU with its two coefficients already formed: z > 0: a_pos z^2 + z/2; z <= 0: a_neg (exp(z) - 1 - z) + z/2.
+__device__ __forceinline__ float xielu(float z, float a_pos, float a_neg) {
+    return z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 

@@ -40,6 +40,7 @@ typedef int (*AttnDecodeFusedFn)(const LlmeFastAttnArgs*, const LlmeFusedQkv*, c
 typedef long long (*AttnScratchFn)(int, int, int);
 typedef int (*AttnTcFn)(const void*, long long, long long, const LlmeTcAttnArgs*, int, cudaStream_t);
 typedef const char* (*LastErrorFn)();
+typedef int (*GemmActFn)(const void*, long long, const void*, long long, void*, int, long long, int, int, int, int, float, float, cudaStream_t);
 typedef int (*XieluFn)(const void*, long long, void*, long long, int, int, int, float, float, cudaStream_t);
 typedef int (*SigmoidMulFn)(const void*, long long, const void*, long long, void*, long long, int, int, int, cudaStream_t);
 typedef int (*ResidualAddFn)(float*, const void*, const void*, int, void*, int, int, int, cudaStream_t);
@@ -451,9 +452,17 @@ int op_linear_act(LlmeExecutor& ex, const LlmeLinearActOp& o, const LlmeStep& s,
     const int M = s.num_tokens;
     if (M <= 0) return 0;
     const LlmeLinearOp& p = o.product;
+    if (o.act != LLME_ACT_XIELU) return ex.fail("linear_act: unknown activation %d", o.act);
+    // a handful of tokens: the weight-streaming product carries the activation in its epilogue (same rule as the plain product)
+    const std::string& dec = ex.choice("linear.decode");
+    if (p.x_dtype == LLME_DT_BF16 && p.w_dtype == LLME_DT_BF16 && ex.choice("linear") != "plain" && ex.choice("linear_swiglu") == "fused" &&
+        M <= SKINNY_ROWS && p.k % 8 == 0 && p.ldx % 8 == 0 && p.ldw % 8 == 0 && aligned16(p.x, p.w) &&
+        (dec == "skinny" || (dec == "auto" && skinny_pays(ex, M, (p.n + 15) / 16)))) {
+        if (auto* f = (GemmActFn)ex.find("gemm_skinny_act"))
+            return ex.launched(f(p.x, p.ldx, p.w, p.ldw, o.out, p.out_dtype, o.ldo, M, p.n, p.k, o.act, o.p0, o.p1, st), "gemm_skinny_act");
+    }
     if (!p.out) return ex.fail("linear_act: the product needs its workspace");
     if (int rc = product(ex, s, p.x, p.ldx, p.x_dtype, p.w, p.ldw, p.w_dtype, p.out, p.ldo, p.out_dtype, M, p.n, p.k, st)) return rc;
-    if (o.act != LLME_ACT_XIELU) return ex.fail("linear_act: unknown activation %d", o.act);
     auto* f = (XieluFn)ex.find("xielu");
     if (!f) return ex.fail("no xielu kernel is registered");
     return ex.launched(f(p.out, p.ldo, o.out, o.ldo, p.out_dtype, M, p.n, o.p0, o.p1, st), "xielu");

@@ -53,6 +53,8 @@ struct SkinnyArgs {
     void* out; long long ldo;
     int M, N, K;
     int inter;      // 0: plain product; > 0: W = [gate | up] of `inter` rows each and out = silu(gate) * up
+    int pointwise;  // with inter == 0: 0 = none, 1 = xIELU of the product (through bfloat16 first), coefficients p0, p1
+    float p0, p1;
 };
 
 // MT: 8-token tiles (1: M <= 8, 2: M <= 16).  Every block of a token's row re-reads the tokens' operands from L2, so
@@ -157,7 +159,12 @@ __global__ void __launch_bounds__(THREADS, BLOCKS) gemm_skinny_kernel(SkinnyArgs
     if (!act) {
         for (int i = threadIdx.x; i < MT * 8 * 16; i += THREADS) {
             const int tok = i >> 4, row = rg * 16 + (i & 15);
-            if (tok < a.M && row < a.N) reinterpret_cast<O*>(a.out)[(size_t)tok * a.ldo + row] = from_f32<O>(total(i));
+            if (tok < a.M && row < a.N) {
+                float v = total(i);
+                // the activation sees the product as it is stored when the activation is a kernel of its own
+                if (a.pointwise == 1) v = xielu(__bfloat162float(__float2bfloat16_rn(v)), a.p0, a.p1);
+                reinterpret_cast<O*>(a.out)[(size_t)tok * a.ldo + row] = from_f32<O>(v);
+            }
         }
     } else {
         // rows 0..7 of the group are gate rows, rows 8..15 the up rows of the same outputs; both go through
@@ -226,7 +233,7 @@ LLME_API int llme_gemm_skinny_bf16(const void* x, long long ldx, const void* w, 
     if (!llme_gemm_skinny_supports(M, N, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d N=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 16, K and strides multiples of 8)", M, N, K, ldx, ldw);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (ldo < N) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");
-    SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, N, K, 0};
+    SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, N, K, 0, 0, 0.0f, 0.0f};
     if (out_dtype == LLME_F32) return dispatch<float>(a, stream);
     if (out_dtype == LLME_BF16) return dispatch<bf16>(a, stream);
     LLME_REFUSE("gemm_skinny: unsupported output dtype %d", out_dtype);
@@ -240,7 +247,22 @@ LLME_API int llme_gemm_skinny_swiglu_bf16(const void* x, long long ldx, const vo
     if (inter > (1 << 29) || !llme_gemm_skinny_supports(M, 2 * inter, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d inter=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 16, K and strides multiples of 8)", M, inter, K, ldx, ldw);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (ldo < inter) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");
-    SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, 2 * inter, K, inter};
+    SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, 2 * inter, K, inter, 0, 0.0f, 0.0f};
+    if (out_dtype == LLME_F32) return dispatch<float>(a, stream);
+    if (out_dtype == LLME_BF16) return dispatch<bf16>(a, stream);
+    LLME_REFUSE("gemm_skinny: unsupported output dtype %d", out_dtype);
+}
+
+// out[M, N] = act(x W^T), elementwise, in the product's epilogue.  act 1: xIELU with coefficients p0 (z > 0) and p1 (z <= 0).
+LLME_API int llme_gemm_skinny_act_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
+                                       long long ldo, int M, int N, int K, int act, float p0, float p1, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (!x || !w || !out) LLME_REFUSE("gemm_skinny: null pointer");
+    if (act != 1) LLME_REFUSE("gemm_skinny: unknown activation %d", act);
+    if (!llme_gemm_skinny_supports(M, N, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d N=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 16, K and strides multiples of 8)", M, N, K, ldx, ldw);
+    if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
+    if (ldo < N) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");
+    SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, N, K, 0, act, p0, p1};
     if (out_dtype == LLME_F32) return dispatch<float>(a, stream);
     if (out_dtype == LLME_BF16) return dispatch<bf16>(a, stream);
     LLME_REFUSE("gemm_skinny: unsupported output dtype %d", out_dtype);

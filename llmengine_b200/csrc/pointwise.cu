@@ -8,11 +8,6 @@
 
 LLME_API const char* llme_last_error() { return llme_error_buffer(); }
 
-// xIELU with its two coefficients already formed: z > 0: a_pos z^2 + z/2; z <= 0: a_neg (exp(z) - 1 - z) + z/2.
-__device__ __forceinline__ float xielu(float z, float a_pos, float a_neg) {
-    return z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);
-}
-
 __device__ __forceinline__ float gelu_tanh(float z) {
     const float k = 0.7978845608028654f;                 // sqrt(2 / pi)
     return 0.5f * z * (1.0f + tanhf(k * (z + 0.044715f * z * z * z)));

@@ -14,7 +14,7 @@ from llmengine_b200.config import BepuzenConfig, ConfigError, config_from_dict
 from llmengine_b200.engine.model import Model
 from llmengine_b200.parts import Runtime
 from plain_bepuzen import PlainBepuzen
-from tiny_bepuzen import ONLY_L1, TINY_P, TINY_Q, make_bepuzen_dir, tensor_shapes
+from tiny_bepuzen import ONLY_L1, TINY_P, TINY_Q, TINY_S, make_bepuzen_dir, tensor_shapes
 
 
 def test_every_size_and_constant_comes_from_the_file():
@@ -40,14 +40,14 @@ def test_every_size_and_constant_comes_from_the_file():
         config_from_dict(d)
 
 
-@pytest.mark.parametrize("cfg", [TINY_P, TINY_Q, ONLY_L1])
+@pytest.mark.parametrize("cfg", [TINY_P, TINY_Q, TINY_S, ONLY_L1])
 def test_the_model_declares_the_design_s_tensors(cfg):
     model = Model(config_from_dict(cfg).model_spec(), Runtime(None, torch.device("cpu"), torch.float32, 1))
     declared = {n: tuple(s.shape) for n, s in model.weight_specs().items()}
     assert declared == tensor_shapes(cfg)
 
 
-@pytest.mark.parametrize("name,cfg,page", [("P", TINY_P, 16), ("Q", TINY_Q, 8)])
+@pytest.mark.parametrize("name,cfg,page", [("P", TINY_P, 16), ("Q", TINY_Q, 8), ("S", TINY_S, 32)])
 def test_host_logic_replay_cpu(tmp_path, name, cfg, page):
     d = make_bepuzen_dir(str(tmp_path / name), cfg, seed=3)
     replay_all_schedules(d, cfg, "float32", [70, 33, 100, 1, 19, 45], page, HostOps(), "cpu")

@@ -13,7 +13,8 @@ import torch
 from bepuzen_cases import TOL_F32, greedy_by_the_plain_model, reference_logits, replay_all_schedules, schedules
 from helpers import compare, engine_for, max_live_tokens, random_ids, replay, trace_bulk_then_single, trace_whole
 from plain_bepuzen import PlainBepuzen, gelu_tanh, token_side_input, xielu
-from tiny_bepuzen import (L2, ONLY_L1, ONLY_L2, TINY_P, TINY_Q, TINY_R, WITH_FF, WITH_SIDE, layer, make_bepuzen_dir, mixer2)
+from tiny_bepuzen import (L2, ONLY_L1, ONLY_L2, TINY_P, TINY_Q, TINY_R, TINY_S, WITH_FF, WITH_SIDE, layer, make_bepuzen_dir,
+                          mixer2)
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -39,11 +40,12 @@ def _softplus(v):
 
 
 # ----------------------------------------------------------------------------- single kernels
+@pytest.mark.parametrize("T", [5, 37])      # a handful of tokens: the activation rides in the product's epilogue
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
-def test_pointwise_kernels(dtype, tol):
+def test_pointwise_kernels(dtype, tol, T):
     ops = _ops()
     g = torch.Generator().manual_seed(1)
-    T, K, N = 37, 40, 52
+    K, N = 40, 52
     x = (torch.randn(T, K, generator=g)).to(dtype)
     w = (torch.randn(N, K, generator=g) / 4).to(dtype)
     pq = torch.tensor([0.3, -1.1])
@@ -116,6 +118,7 @@ def test_each_mechanism_alone(tmp_path, name, cfg, dtype):
     ("P", TINY_P, 16, [70, 33, 100, 1, 19, 45, 64]),
     ("Q", TINY_Q, 8, [2, 5, 64, 130, 200, 48]),
     ("R", TINY_R, 64, [300, 129, 40, 520, 128, 17]),
+    ("S", TINY_S, 32, [3, 77, 140, 64, 31, 9]),
 ])
 def test_replay_gpu(tmp_path, name, cfg, page, lens, dtype, kernels):
     d = make_bepuzen_dir(str(tmp_path / name), cfg, seed=11, sharpen=2.0)

@@ -51,6 +51,15 @@ TINY_Q = {
         layer(L1, mixer1(20, 8, 16, 8, 64, 0.2, base=77.0), 0),
     ],
 }
+# odd sizes everywhere: no 16-byte rows, products that only the library takes, a latent size no tensor-core kernel is built for
+TINY_S = {
+    "architecture": "Bepuzen", "vocab": 131, "width": 100, "norm": {"eps": 2e-5}, "token_side": {"dim": 5},
+    "layers": [
+        layer(L1, mixer1(3, 20, 12, 12, 72, 0.27, base=333.0, dims=6), 70),
+        layer(L1, mixer1(5, 6, 10, 14, 40, 0.31, base=9.0), 0),
+        layer(L2, mixer2(7, 10, 6, 56, 0.4), 33),
+    ],
+}
 # one layer of each mixer and nothing else, and single sublayers added to it: each mechanism by itself
 ONLY_L2 = {"architecture": "Bepuzen", "vocab": 61, "width": 48, "norm": {"eps": 1e-6},
            "layers": [layer(L2, mixer2(4, 16, 8, 64, 0.3), 0)]}
