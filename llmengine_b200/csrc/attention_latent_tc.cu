@@ -83,7 +83,9 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
     const int r = a.rows[n];
     const int tok0 = a.cu_q_lens[r], q_len = a.cu_q_lens[r + 1] - tok0;
     const int H = a.nh, n_rows = q_len * H;
-    const int row0 = blockIdx.x * BM;
+    // the last rows of a prompt see the most keys: their blocks are launched first, so that the long ones do not
+    // run alone at the end
+    const int row0 = (int)(gridDim.x - 1 - blockIdx.x) * BM;
     if (row0 >= n_rows) return;
     const int ctx = a.ctx_lens[r], first_pos = ctx - q_len;
     const int last_row = min(row0 + BM, n_rows) - 1;
