@@ -139,6 +139,10 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
     }
     if (t_begin < t_end) load_keys(t_begin, 0);
     cp_async_commit();
+    if (STAGES == 2) {                             // the second tile is requested at once, not when the first has landed
+        if (t_begin + 1 < t_end) load_keys(t_begin + 1, 1);
+        cp_async_commit();
+    }
 
     // this thread's two rows of its group: lane / 4 and lane / 4 + 8
     const int lr0 = rg * 16 + (lane >> 2), lr1 = lr0 + 8;
@@ -162,12 +166,9 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
             load_keys(tile, 0);
             cp_async_commit();
         }
-        cp_async_wait<0>();
+        if (STAGES == 2) cp_async_wait<1>();       // everything but the newest request: this tile has landed
+        else cp_async_wait<0>();
         __syncthreads();
-        if (STAGES == 2) {
-            if (tile + 1 < t_end) load_keys(tile + 1, stage ^ 1);
-            cp_async_commit();
-        }
         const __nv_bfloat16* kt = k_s + (size_t)stage * BN * ld;
 
         // 1. scores of this warp's rows against its share of the tile's keys
@@ -285,6 +286,11 @@ __global__ void __launch_bounds__(WARPS * 32, RG <= 2 ? 2 : 1) latent_attention_
                 ldmatrix_x2_trans(v_addr + (uint32_t)(ks * 16 * ld * 2) + (NT_O - 1) * 16, b0, b1);
                 mma_bf16(o[NT_O - 1], a0, a1, a2, a3, b0, b1);
             }
+        }
+        if (STAGES == 2) {                         // the stage is free again: the tile after the next one goes there
+            __syncthreads();
+            if (tile + 2 < t_end) load_keys(tile + 2, stage);
+            cp_async_commit();
         }
     }
     cp_async_wait<0>();
