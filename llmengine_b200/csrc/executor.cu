@@ -461,6 +461,14 @@ int op_linear_act(LlmeExecutor& ex, const LlmeLinearActOp& o, const LlmeStep& s,
         if (auto* f = (GemmActFn)ex.find("gemm_skinny_act"))
             return ex.launched(f(p.x, p.ldx, p.w, p.ldw, o.out, p.out_dtype, o.ldo, M, p.n, p.k, o.act, o.p0, o.p1, st), "gemm_skinny_act");
     }
+    // many tokens: the tcgen05 product with the activation in its epilogue, where the plain product would take that kernel
+    const std::string& how = ex.choice("linear");
+    if (p.x_dtype == LLME_DT_BF16 && p.w_dtype == LLME_DT_BF16 && ex.choice("linear_swiglu") == "fused" && M >= 128 && p.k % 8 == 0 &&
+        p.ldx % 8 == 0 && p.ldw % 8 == 0 && aligned16(p.x, p.w) && p.n >= 8 && o.ldo >= p.n &&
+        (how == "tcgen05" || (how == "auto" && tc_fills_its_waves(ex, M, p.n)))) {
+        if (auto* f = (GemmActFn)ex.find("gemm_tc_act"))
+            return ex.launched(f(p.x, p.ldx, p.w, p.ldw, o.out, p.out_dtype, o.ldo, M, p.n, p.k, o.act, o.p0, o.p1, st), "gemm_tc_act");
+    }
     if (!p.out) return ex.fail("linear_act: the product needs its workspace");
     if (int rc = product(ex, s, p.x, p.ldx, p.x_dtype, p.w, p.ldw, p.w_dtype, p.out, p.ldo, p.out_dtype, M, p.n, p.k, st)) return rc;
     auto* f = (XieluFn)ex.find("xielu");

@@ -39,6 +39,8 @@ struct TcArgs {
     int M, N, K;
     int m_tiles, n_tiles;
     int inter;      // ACT kernels: W = [gate | up] with `inter` rows each, out[M, inter] = silu(gate) * up
+    int pointwise;  // other kernels: 0 = the product as it is; 1 = xIELU of it (through bfloat16 first), coefficients p0, p1
+    float p0, p1;
 };
 
 // Persistent kernel: one block per SM walks over the output tiles (m fastest, so blocks that run together
@@ -231,6 +233,12 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap& map_x, const CUt
                         }
                     } else {
                         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (a.pointwise == 1) {
+                            // an activation of one argument: it sees the product as a kernel of its own would read it
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                v[j] = __float_as_uint(xielu_bf16(__bfloat162float(__float2bfloat16_rn(__uint_as_float(v[j]))), a.p0, a.p1));
+                        }
                     }
                     if (c + COLS >= OUT_COLS && half == COLS / 32 - 1) {
                         // the tile has left tensor memory: hand the buffer back to the MMA warp
@@ -386,6 +394,8 @@ LLME_API int llme_gemm_tc_supports(int M, int N, int K, long long ldx, long long
     return M >= 1 && N >= 8 && K >= 8 && K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0 && ldo >= N;
 }
 
+static int run_plain(const void* x, long long ldx, const void* w, long long ldw, TcArgs a, int out_dtype, cudaStream_t stream);
+
 // x [M,K], W [N,K] bfloat16 (row strides ldx, ldw in elements, base addresses 16-byte aligned);
 // out [M,N] float (out_dtype 0) or bfloat16 (1), row stride ldo.
 LLME_API int llme_gemm_tc_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
@@ -394,7 +404,12 @@ LLME_API int llme_gemm_tc_bf16(const void* x, long long ldx, const void* w, long
     if (!x || !w || !out) LLME_REFUSE("gemm_tc: null pointer");
     if (!llme_gemm_tc_supports(M, N, K, ldx, ldw, ldo)) LLME_REFUSE("gemm_tc: M=%d N=%d K=%d ldx=%lld ldw=%lld ldo=%lld is not supported (K and operand strides must be multiples of 8)", M, N, K, ldx, ldw, ldo);
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_tc: operands must be 16-byte aligned");
-    TcArgs a{out, ldo, M, N, K, 0, 0, 0};
+    TcArgs a{out, ldo, M, N, K, 0, 0, 0, 0, 0.0f, 0.0f};
+    return run_plain(x, ldx, w, ldw, a, out_dtype, stream);
+}
+
+static int run_plain(const void* x, long long ldx, const void* w, long long ldw, TcArgs a, int out_dtype, cudaStream_t stream) {
+    const int M = a.M, N = a.N;
     const bool pairs = use_pairs(M, N, g_pairing);
     if (out_dtype == LLME_F32) {
         if (pairs) return launch<256, 6, float, true>(x, ldx, w, ldw, a, stream);
@@ -405,6 +420,18 @@ LLME_API int llme_gemm_tc_bf16(const void* x, long long ldx, const void* w, long
         return N > 128 ? launch<256, 4, bf16, false>(x, ldx, w, ldw, a, stream) : launch<128, 6, bf16, false>(x, ldx, w, ldw, a, stream);
     }
     LLME_REFUSE("gemm_tc: unsupported output dtype %d", out_dtype);
+}
+
+// out[M, N] = act(x W^T) elementwise, in the epilogue.  act 1: xIELU with coefficients p0 (z > 0) and p1 (z <= 0).
+LLME_API int llme_gemm_tc_act_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
+                                   long long ldo, int M, int N, int K, int act, float p0, float p1, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (!x || !w || !out) LLME_REFUSE("gemm_tc: null pointer");
+    if (act != 1) LLME_REFUSE("gemm_tc: unknown activation %d", act);
+    if (!llme_gemm_tc_supports(M, N, K, ldx, ldw, ldo)) LLME_REFUSE("gemm_tc: M=%d N=%d K=%d ldx=%lld ldw=%lld ldo=%lld is not supported (K and operand strides must be multiples of 8)", M, N, K, ldx, ldw, ldo);
+    if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_tc: operands must be 16-byte aligned");
+    TcArgs a{out, ldo, M, N, K, 0, 0, 0, act, p0, p1};
+    return run_plain(x, ldx, w, ldw, a, out_dtype, stream);
 }
 
 // 0: pairs of blocks (tcgen05 with .cta_group::2) where they pay; 1: never; 2: always.  For tests and measurements.
@@ -425,7 +452,7 @@ LLME_API int llme_gemm_tc_swiglu_bf16(const void* x, long long ldx, const void* 
     if (!x || !w || !out) LLME_REFUSE("gemm_tc: null pointer");
     if (!llme_gemm_tc_swiglu_supports(M, inter, K, ldx, ldw, ldo)) LLME_REFUSE("gemm_tc: M=%d inter=%d K=%d ldx=%lld ldw=%lld ldo=%lld is not supported (K and strides must be multiples of 8)", M, inter, K, ldx, ldw, ldo);
     if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) % 16) LLME_REFUSE("gemm_tc: operands and output must be 16-byte aligned");
-    TcArgs a{out, ldo, M, 2 * inter, K, 0, 0, inter};
+    TcArgs a{out, ldo, M, 2 * inter, K, 0, 0, inter, 0, 0.0f, 0.0f};
     if (use_pairs(M, 2 * inter, g_pairing)) return launch_act<256, 6, bf16, true>(x, ldx, w, ldw, a, stream);
     return launch_act<256, 4, bf16, false>(x, ldx, w, ldw, a, stream);
 }

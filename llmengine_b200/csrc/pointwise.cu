@@ -36,11 +36,35 @@ static dim3 grid_for(int rows, int cols, int threads) {
     return dim3(rows, pieces < 1 ? 1 : pieces);
 }
 
+// bfloat16 rows of whole 16-byte pieces: eight values per thread and load
+__global__ void xielu_bf16x8_kernel(const __nv_bfloat16* __restrict__ in, long long ld_in, __nv_bfloat16* __restrict__ out, long long ld_out,
+                                    int cols, float a_pos, float a_neg) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint4* i = reinterpret_cast<const uint4*>(in + (size_t)blockIdx.x * ld_in);
+    uint4* o = reinterpret_cast<uint4*>(out + (size_t)blockIdx.x * ld_out);
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols / 8; j += gridDim.y * blockDim.x) {
+        uint4 v = i[j];
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            h[e] = __floats2bfloat162_rn(xielu_bf16(f.x, a_pos, a_neg), xielu_bf16(f.y, a_pos, a_neg));
+        }
+        o[j] = v;
+    }
+}
+
 LLME_API int llme_xielu(const void* in, long long ld_in, void* out, long long ld_out, int dtype, int rows, int cols,
                         float a_pos, float a_neg, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (!in || !out) LLME_REFUSE("xielu: null pointer");
     const int threads = 128;
+    if (dtype == LLME_BF16 && cols % 8 == 0 && ld_in % 8 == 0 && ld_out % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0) {
+        llme_launch(xielu_bf16x8_kernel, grid_for(rows, cols / 8, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)in, ld_in,
+                    (__nv_bfloat16*)out, ld_out, cols, a_pos, a_neg);
+        LLME_LAUNCH_STATUS();
+    }
     if (dtype == LLME_F32) llme_launch(xielu_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)in, ld_in, (float*)out, ld_out, cols, a_pos, a_neg);
     else if (dtype == LLME_BF16) llme_launch(xielu_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)in, ld_in, (__nv_bfloat16*)out, ld_out, cols, a_pos, a_neg);
     else LLME_REFUSE("xielu: unsupported dtype %d", dtype);

@@ -197,7 +197,8 @@ class CudaOps:
                                 "latent_attention_tc_fits/{hd}": "llme_latent_attention_tc_fits"},
         "gemm_skinny": {"gemm_skinny": "llme_gemm_skinny_bf16", "gemm_skinny_swiglu": "llme_gemm_skinny_swiglu_bf16",
                         "gemm_skinny_act": "llme_gemm_skinny_act_bf16"},
-        "gemm_tcgen05": {"gemm_tc": "llme_gemm_tc_bf16", "gemm_tc_swiglu": "llme_gemm_tc_swiglu_bf16"},
+        "gemm_tcgen05": {"gemm_tc": "llme_gemm_tc_bf16", "gemm_tc_swiglu": "llme_gemm_tc_swiglu_bf16",
+                         "gemm_tc_act": "llme_gemm_tc_act_bf16"},
         "attention_plain": {"attention_plain": "llme_attention_plain"},
         "attention_fast": {"attention_portion/{hd}": "llme_attention_portion", "attention_decode/{hd}": "llme_attention_decode",
                            "attention_decode_fused/{hd}": "llme_attention_decode_fused",
