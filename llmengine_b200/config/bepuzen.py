@@ -105,7 +105,7 @@ class BepuzenConfig:
                 if kw["rot_dims"] % 2 or kw["rot_dims"] > kw["rot_dim"]:
                     raise ConfigError(f"{mat}rot.dims={kw['rot_dims']} must be even and at most rot_dim={kw['rot_dim']}")
             mixers.append(LatentMixerConfig(**kw))
-            mlp = _need(L, "mlp", at)
+            mlp = L.get("mlp")                   # null, or no such key: the layer has no feed-forward
             if mlp is None:
                 ffs.append(0)
             else:

@@ -26,7 +26,7 @@ def test_every_size_and_constant_comes_from_the_file():
     assert config_from_dict(c.to_dict()) == c
     assert config_from_dict(TINY_Q).side_dim == 0
     for path in (["width"], ["norm"], ["layers", 0, "mixer", "kv_rank"], ["layers", 0, "mixer", "rot", "base"],
-                 ["layers", 1, "mlp"], ["layers", 2, "type"], ["token_side", "dim"], ["layers", 0, "mixer", "scale"]):
+                 ["layers", 0, "mlp", "ff"], ["layers", 2, "type"], ["token_side", "dim"], ["layers", 0, "mixer", "scale"]):
         d = copy.deepcopy(TINY_P)
         at = d
         for k in path[:-1]:
@@ -34,6 +34,9 @@ def test_every_size_and_constant_comes_from_the_file():
         del at[path[-1]]
         with pytest.raises(ConfigError, match=str(path[-1])):
             config_from_dict(d)
+    d = copy.deepcopy(TINY_P)
+    del d["layers"][1]["mlp"]                       # no key at all reads like null: no feed-forward
+    assert config_from_dict(d) == c
     d = copy.deepcopy(TINY_P)
     d["layers"][1]["type"] = "something_else"
     with pytest.raises(ConfigError, match="something_else"):
