@@ -83,9 +83,15 @@ class Group:
     runs: List[int] = field(default_factory=list)
     max_blocks: int = 0
     committed: int = 0                # pages promised to admitted requests (admission control)
+    keep_first: int = 0               # with a window: the first positions of a request that every later query still sees
+
+    @property
+    def kept_blocks(self) -> int:
+        """Blocks at the start of a request that are never given back (they hold its first `keep_first` positions)."""
+        return -(-self.keep_first // self.page_size) if self.window > 0 else 0
 
     def first_needed_block(self, length: int) -> int:
-        """Blocks below this index hold only positions that no later query can see."""
+        """Blocks below this index (and from `kept_blocks` on) hold only positions that no later query can see."""
         if self.window <= 0:
             return 0
         return max(0, length - self.window + 1) // self.page_size
@@ -97,7 +103,7 @@ class Group:
         if self.window <= 0:
             return full
         span = self.window - 1 + max_portion
-        return min(full, -(-span // self.page_size) + 1)
+        return min(full, -(-span // self.page_size) + 1 + self.kept_blocks)
 
 
 @dataclass
@@ -127,7 +133,7 @@ class CacheManager:
         self.groups: List[Group] = []
         self.run_group: List[Optional[int]] = []     # run -> group index (paged runs)
         self.run_owner: List[int] = []               # run -> run whose tensor it uses
-        by_key: Dict[Tuple[int, int], int] = {}
+        by_key: Dict[Tuple[int, int, int], int] = {}
         num_pages = -(-max_cached_tokens // page_size)
         max_blocks = -(-max_request_len // page_size)
         for i, (spec, cache_from) in enumerate(self.specs):
@@ -140,10 +146,11 @@ class CacheManager:
                 self.run_group.append(self.run_group[cache_from])
                 continue
             if spec is not None and getattr(spec, "paged", False):
-                key = (page_size, int(getattr(spec, "window", 0)))
+                window = int(getattr(spec, "window", 0))
+                key = (page_size, window, int(getattr(spec, "keep_first", 0)) if window > 0 else 0)
                 if key not in by_key:
                     by_key[key] = len(self.groups)
-                    self.groups.append(Group(page_size, key[1], PagePool(num_pages), max_blocks=max_blocks))
+                    self.groups.append(Group(page_size, key[1], PagePool(num_pages), max_blocks=max_blocks, keep_first=key[2]))
                 self.groups[by_key[key]].runs.append(i)
                 self.run_group.append(by_key[key])
             else:
@@ -278,7 +285,7 @@ class CacheManager:
         st.length = new_length
         for gi, g in enumerate(self.groups):
             stop = min(g.first_needed_block(new_length), len(st.blocks[gi]))
-            gone = [(b, p) for b, p in enumerate(st.blocks[gi][:stop]) if p >= 0]
+            gone = [(b, p) for b, p in enumerate(st.blocks[gi][:stop]) if p >= 0 and b >= g.kept_blocks]
             if gone:
                 g.pool.free([p for _, p in gone])
                 for b, _ in gone:

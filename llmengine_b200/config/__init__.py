@@ -10,6 +10,7 @@ from typing import Any, Callable, Dict, Mapping, Optional, Type
 from .bepuzen import BepuzenConfig
 from .qwen3 import ConfigError, Qwen3Config
 from .spec import LayerRun, LayerSpec, ModelSpec, PartSpec
+from .torisun import TorisunConfig
 
 
 @dataclass(frozen=True)
@@ -67,6 +68,7 @@ def load_config(model_dir: str):
 
 register_architecture(Qwen3Config.ARCHITECTURE, Qwen3Config)
 register_architecture(BepuzenConfig.ARCHITECTURE, BepuzenConfig)
+register_architecture(TorisunConfig.ARCHITECTURE, TorisunConfig)
 
 
 @dataclass
@@ -115,5 +117,5 @@ class EngineConfig:
 
 __all__ = [
     "ARCHITECTURES", "Architecture", "BepuzenConfig", "ConfigError", "EngineConfig", "LayerRun", "LayerSpec", "ModelSpec",
-    "PartSpec", "Qwen3Config", "config_from_dict", "find_architecture", "load_config", "register_architecture",
+    "PartSpec", "Qwen3Config", "TorisunConfig", "config_from_dict", "find_architecture", "load_config", "register_architecture",
 ]

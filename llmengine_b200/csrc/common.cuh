@@ -91,6 +91,14 @@ inline cudaError_t llme_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
 // issues the matrix instructions.  The 32-bit path keeps expf and the division.
 __device__ __forceinline__ float silu_mul_bf16(float g, float u) { return (g * __frcp_rn(1.0f + __expf(-g))) * u; }
 
+// The clamped gate of some designs, for values that have been through bfloat16 and go back to it:
+// g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).
+__device__ __forceinline__ float clamped_swish_mul_bf16(float g, float u, float limit, float slope) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return (g * __frcp_rn(1.0f + __expf(-slope * g))) * (u + 1.0f);
+}
+
 // xIELU with its two coefficients already formed: z > 0: a_pos z^2 + z/2; z <= 0: a_neg (exp(z) - 1 - z) + z/2.
 __device__ __forceinline__ float xielu(float z, float a_pos, float a_neg) {
     return z > 0.0f ? fmaf(a_pos * z, z, 0.5f * z) : fmaf(a_neg, expm1f(z) - z, 0.5f * z);

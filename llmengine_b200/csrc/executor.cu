@@ -50,6 +50,15 @@ typedef int (*LatentPostFn)(const LlmeLatentPostArgs*, int, cudaStream_t);
 typedef int (*LatentAttnPlainFn)(const LlmeLatentAttnArgs*, int, cudaStream_t);
 typedef int (*LatentAttnTcFn)(const LlmeFastAttnArgs*, const float*, int, int, cudaStream_t);
 typedef int (*LatentFitsFn)(int);
+typedef int (*PostNormFn)(float*, const void*, int, const void*, int, void*, int, int, int, float, int, cudaStream_t);
+typedef int (*GatedActFn)(const void*, long long, void*, long long, int, int, int, int, float, float, cudaStream_t);
+typedef int (*GemmGatedFn)(const void*, long long, const void*, long long, void*, int, long long, int, int, int, int, float, float, cudaStream_t);
+typedef int (*WindowPostFn)(const LlmeWindowPostArgs*, int, cudaStream_t);
+typedef int (*WindowAttnPlainFn)(const LlmeWindowAttnArgs*, int, cudaStream_t);
+typedef int (*WindowAttnTcFn)(const LlmeWindowFastArgs*, int, int, cudaStream_t);
+typedef int (*MoeRouteFn)(const LlmeMoeRouteArgs*, cudaStream_t);
+typedef int (*GroupedFn)(const LlmeGroupedArgs*, int, int, int, cudaStream_t);
+typedef int (*MoeCombineFn)(const float*, long long, const float*, const float*, float*, int, int, int, cudaStream_t);
 typedef int (*GemmF32BatchedFn)(const float*, const void*, int, float*, int, int, int, long long, long long, long long, int, long long,
                                 long long, long long, cudaStream_t);
 
@@ -156,13 +165,19 @@ size_t record_size(int kind) {
         case LLME_OP_RESIDUAL_ADD: return sizeof(LlmeResidualAddOp);
         case LLME_OP_LATENT_ATTENTION: return sizeof(LlmeLatentAttentionOp);
         case LLME_OP_TOKEN_SIDE: return sizeof(LlmeTokenSideOp);
+        case LLME_OP_POSTNORM: return sizeof(LlmePostNormOp);
+        case LLME_OP_WINDOW_ATTENTION: return sizeof(LlmeWindowAttentionOp);
+        case LLME_OP_MOE_ROUTE: return sizeof(LlmeMoeRouteOp);
+        case LLME_OP_GROUPED_LINEAR: return sizeof(LlmeGroupedLinearOp);
+        case LLME_OP_MOE_COMBINE: return sizeof(LlmeMoeCombineOp);
     }
     return 0;
 }
 const char* kind_name(int kind) {
     static const char* names[] = {"?", "embedding", "rmsnorm", "linear", "linear_swiglu", "qkv_post", "attend", "attention", "call",
-                                  "linear_act", "pointwise", "batched_linear", "residual_add", "latent_attention", "token_side"};
-    return kind >= 1 && kind <= 14 ? names[kind] : names[0];
+                                  "linear_act", "pointwise", "batched_linear", "residual_add", "latent_attention", "token_side",
+                                  "postnorm", "window_attention", "moe_route", "grouped_linear", "moe_combine"};
+    return kind >= 1 && kind <= 19 ? names[kind] : names[0];
 }
 
 constexpr int SKINNY_ROWS = 16;      // most rows the weight-streaming product takes (gemm_skinny.cu)
@@ -295,7 +310,10 @@ int op_linear_swiglu(LlmeExecutor& ex, const LlmeLinearSwigluOp& o, const LlmeSt
     const bool operands_ok = o.k % 8 == 0 && o.ldx % 8 == 0 && o.ldw % 8 == 0 && aligned16(o.x, o.w_gate_up);
     const std::string& dec = ex.choice("linear.decode");
     if (fused && M <= SKINNY_ROWS && operands_ok && (dec == "skinny" || (dec == "auto" && skinny_pays(ex, M, (o.inter + 7) / 8)))) {
-        if (auto* f = (GemmBf16Fn)ex.find("gemm_skinny_swiglu"))
+        if (o.act != LLME_GATE_SILU) {
+            if (auto* f = (GemmGatedFn)ex.find("gemm_skinny_gated"))
+                return ex.launched(f(o.x, o.ldx, o.w_gate_up, o.ldw, o.out, LLME_DT_BF16, o.ldo, M, o.inter, o.k, o.act, o.p0, o.p1, st), "gemm_skinny_gated");
+        } else if (auto* f = (GemmBf16Fn)ex.find("gemm_skinny_swiglu"))
             return ex.launched(f(o.x, o.ldx, o.w_gate_up, o.ldw, o.out, LLME_DT_BF16, o.ldo, M, o.inter, o.k, st), "gemm_skinny_swiglu");
     }
     // the tcgen05 kernel with the activation in its epilogue: its tile is 128 tokens x (128 gate + 128 up) rows; like
@@ -304,12 +322,20 @@ int op_linear_swiglu(LlmeExecutor& ex, const LlmeLinearSwigluOp& o, const LlmeSt
     const std::string& how = ex.choice("linear");
     if (fused && M >= 128 && operands_ok && o.inter >= 8 && o.ldo % 8 == 0 && aligned16(o.out) &&
         (how == "tcgen05" || (how == "auto" && tc_fills_its_waves(ex, M, 2 * o.inter)))) {
-        if (auto* f = (GemmTcSwigluFn)ex.find("gemm_tc_swiglu"))
+        if (o.act != LLME_GATE_SILU) {
+            if (auto* f = (GemmGatedFn)ex.find("gemm_tc_gated"))
+                return ex.launched(f(o.x, o.ldx, o.w_gate_up, o.ldw, o.out, LLME_DT_BF16, o.ldo, M, o.inter, o.k, o.act, o.p0, o.p1, st), "gemm_tc_gated");
+        } else if (auto* f = (GemmTcSwigluFn)ex.find("gemm_tc_swiglu"))
             return ex.launched(f(o.x, o.ldx, o.w_gate_up, o.ldw, o.out, o.ldo, M, o.inter, o.k, st), "gemm_tc_swiglu");
     }
     if (!o.gate_up) return ex.fail("linear_swiglu: the unfused form needs a workspace for gate|up");
     if (int rc = product(ex, s, o.x, o.ldx, o.dtype, o.w_gate_up, o.ldw, o.dtype, o.gate_up, 2LL * o.inter, o.dtype, M, 2 * o.inter, o.k, st))
         return rc;
+    if (o.act != LLME_GATE_SILU) {
+        auto* g = (GatedActFn)ex.find("gated_act");
+        if (!g) return ex.fail("no gated activation kernel is registered");
+        return ex.launched(g(o.gate_up, 2LL * o.inter, o.out, o.ldo, o.dtype, M, o.inter, o.act, o.p0, o.p1, st), "gated_act");
+    }
     auto* f = (SwigluFn)ex.find("swiglu");
     if (!f) return ex.fail("no swiglu kernel is registered");
     if (o.ldo != o.inter) return ex.fail("linear_swiglu: the unfused form writes dense rows");
@@ -587,6 +613,78 @@ int op_token_side(LlmeExecutor& ex, const LlmeTokenSideOp& o, const LlmeStep& s,
     return ex.launched(norm(o.x, o.y, o.gain, o.gain_dtype, M, o.size, o.eps, st), "rmsnorm_add");
 }
 
+int op_postnorm(LlmeExecutor& ex, const LlmePostNormOp& o, const LlmeStep& s, cudaStream_t st) {
+    auto* f = (PostNormFn)ex.find("postnorm");
+    if (!f) return ex.fail("no postnorm kernel is registered");
+    return ex.launched(f(o.x, o.y, o.y_dtype, o.gain, o.gain_dtype, o.copy, o.copy_dtype, s.num_tokens, o.size, o.eps, o.accumulate, st), "postnorm");
+}
+
+int op_window_attention(LlmeExecutor& ex, const LlmeWindowAttentionOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0) return 0;
+    if (o.group < 0 || o.group >= s.num_groups) return ex.fail("window attention: the step has no cache group %d", o.group);
+    const LlmeStepGroup& g = s.groups[o.group];
+    auto* post = (WindowPostFn)ex.find("window_post");
+    if (!post) return ex.fail("no window_post kernel is registered");
+    LlmeWindowPostArgs p = {};
+    p.q_in = o.q_in; p.k_in = o.k_in; p.v_in = o.v_in; p.q_stride = o.q_stride; p.k_stride = o.k_stride; p.v_stride = o.v_stride;
+    p.q_gain = o.q_gain; p.k_gain = o.k_gain; p.eps = o.eps; p.inv_freq = o.inv_freq; p.rot_dims = o.rot_dims; p.amplitude = o.amplitude;
+    p.positions = s.positions; p.q_out = o.q; p.cache = o.cache; p.slot_mapping = g.slot_mapping;
+    p.tokens = s.num_tokens; p.nh = o.nh; p.nkv = o.nkv; p.dk = o.dk; p.dv = o.dv; p.page_size = g.page_size;
+    if (int rc = ex.launched(post(&p, o.dtype, st), "window_post")) return rc;
+    // bfloat16 with sizes the tensor-core kernel is built for: prompt portions in one launch, single tokens in another
+    auto* tc = (WindowAttnTcFn)ex.find("window_attention_tc/" + std::to_string(o.dk) + "x" + std::to_string(o.dv));
+    if (tc && o.dtype == LLME_DT_BF16 && ex.choice("attention") == "fast" && g.page_size % 16 == 0) {
+        LlmeWindowFastArgs f = {};
+        f.q = o.q; f.cache = o.cache; f.out = o.out; f.sink = o.sink; f.cu_q_lens = s.cu_q_lens; f.ctx_lens = s.ctx_lens;
+        f.table_rows = s.state_slots; f.block_tables = g.block_tables; f.max_blocks = g.max_blocks; f.nh = o.nh; f.nkv = o.nkv;
+        f.page_size = g.page_size; f.window = o.window; f.keep_first = o.keep_first; f.scale = o.scale;
+        if (s.num_portion > 0) {
+            f.rows = s.portion_rows; f.n_rows = s.num_portion;
+            if (int rc = ex.launched(tc(&f, s.max_portion_len, 0, st), "window_attention_tc")) return rc;
+        }
+        if (s.num_decode > 0) {
+            f.rows = s.decode_rows; f.n_rows = s.num_decode;
+            if (int rc = ex.launched(tc(&f, 1, s.max_decode_ctx, st), "window_attention_tc")) return rc;
+        }
+        return 0;
+    }
+    auto* plain = (WindowAttnPlainFn)ex.find("window_attention_plain");
+    if (!plain) return ex.fail("no window attention kernel is registered");
+    LlmeWindowAttnArgs a = {o.q, o.cache, o.out, o.sink, s.positions, s.token_request, g.block_tables, g.max_blocks, s.num_tokens,
+                            o.nh, o.nkv, o.dk, o.dv, g.page_size, o.window, o.keep_first, o.scale};
+    return ex.launched(plain(&a, o.dtype, st), "window_attention_plain");
+}
+
+int op_moe_route(LlmeExecutor& ex, const LlmeMoeRouteOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0) return 0;
+    auto* f = (MoeRouteFn)ex.find("moe_route");
+    if (!f) return ex.fail("no moe_route kernel is registered");
+    LlmeMoeRouteArgs a = {o.logits, o.ld, s.num_tokens, o.num_experts, o.top_k, o.scale, o.experts, o.weights, o.offsets, o.order, o.counts};
+    const int rc = ex.launched(f(&a, st), "moe_route");
+    ++ex.launches;                                          // routing and ordering are two kernels
+    return rc;
+}
+
+int op_grouped_linear(LlmeExecutor& ex, const LlmeGroupedLinearOp& o, const LlmeStep& s, cudaStream_t st) {
+    if (s.num_tokens <= 0) return 0;
+    LlmeGroupedArgs a = {o.x, o.ldx, o.w, o.ldw, o.w_expert, o.out, o.ldo, o.offsets, o.order, s.num_tokens * o.top_k, o.num_experts,
+                         o.top_k, o.n, o.k, o.gather, o.scatter, o.act};
+    // bfloat16 operands in whole 16-byte pieces: the tensor-core form (the activation in its epilogue)
+    auto* tc = (GroupedFn)ex.find("grouped_linear_tc");
+    if (tc && o.x_dtype == LLME_DT_BF16 && o.w_dtype == LLME_DT_BF16 && ex.choice("linear") != "plain" && o.k % 8 == 0 && o.ldx % 8 == 0 &&
+        o.ldw % 8 == 0 && o.w_expert % 8 == 0 && aligned16(o.x, o.w))
+        return ex.launched(tc(&a, o.x_dtype, o.w_dtype, o.out_dtype, st), "grouped_linear_tc");
+    auto* f = (GroupedFn)ex.find("grouped_linear");
+    if (!f) return ex.fail("no grouped_linear kernel is registered");
+    return ex.launched(f(&a, o.x_dtype, o.w_dtype, o.out_dtype, st), "grouped_linear");
+}
+
+int op_moe_combine(LlmeExecutor& ex, const LlmeMoeCombineOp& o, const LlmeStep& s, cudaStream_t st) {
+    auto* f = (MoeCombineFn)ex.find("moe_combine");
+    if (!f) return ex.fail("no moe_combine kernel is registered");
+    return ex.launched(f(o.y, o.ldy, o.weights, o.base, o.out, s.num_tokens, o.top_k, o.size, st), "moe_combine");
+}
+
 const std::map<std::string, std::vector<std::string>>& variants() {
     static const std::map<std::string, std::vector<std::string>> v = {
         {"linear", {"auto", "tcgen05", "cublas", "plain"}},
@@ -731,6 +829,11 @@ LLME_EXPORT int llme_plan_run(LlmePlan* p, const LlmeStep* step, int first, int 
             case LLME_OP_RESIDUAL_ADD: rc = op_residual_add(ex, *(const LlmeResidualAddOp*)b, s, stream); break;
             case LLME_OP_LATENT_ATTENTION: rc = op_latent_attention(ex, *(const LlmeLatentAttentionOp*)b, s, stream); break;
             case LLME_OP_TOKEN_SIDE: rc = op_token_side(ex, *(const LlmeTokenSideOp*)b, s, stream); break;
+            case LLME_OP_POSTNORM: rc = op_postnorm(ex, *(const LlmePostNormOp*)b, s, stream); break;
+            case LLME_OP_WINDOW_ATTENTION: rc = op_window_attention(ex, *(const LlmeWindowAttentionOp*)b, s, stream); break;
+            case LLME_OP_MOE_ROUTE: rc = op_moe_route(ex, *(const LlmeMoeRouteOp*)b, s, stream); break;
+            case LLME_OP_GROUPED_LINEAR: rc = op_grouped_linear(ex, *(const LlmeGroupedLinearOp*)b, s, stream); break;
+            case LLME_OP_MOE_COMBINE: rc = op_moe_combine(ex, *(const LlmeMoeCombineOp*)b, s, stream); break;
             case LLME_OP_CALL: {
                 const LlmeCallOp& c = *(const LlmeCallOp*)b;
                 rc = c.fn ? c.fn(c.user, step, stream) : 0;

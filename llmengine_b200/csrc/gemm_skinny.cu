@@ -53,7 +53,8 @@ struct SkinnyArgs {
     void* out; long long ldo;
     int M, N, K;
     int inter;      // 0: plain product; > 0: W = [gate | up] of `inter` rows each and out = silu(gate) * up
-    int pointwise;  // with inter == 0: 0 = none, 1 = xIELU of the product (through bfloat16 first), coefficients p0, p1
+    int pointwise;  // with inter == 0: 0 = none, 1 = xIELU of the product (through bfloat16 first), coefficients p0, p1;
+                    // with inter > 0: 0 = silu(gate) * up, 1 = the clamped gate with limit p0 and slope p1
     float p0, p1;
 };
 
@@ -174,7 +175,8 @@ __global__ void __launch_bounds__(THREADS, BLOCKS) gemm_skinny_kernel(SkinnyArgs
             if (tok < a.M && col < a.inter) {
                 const float g = __bfloat162float(__float2bfloat16_rn(total(tok * 16 + j)));
                 const float up = __bfloat162float(__float2bfloat16_rn(total(tok * 16 + j + 8)));
-                reinterpret_cast<O*>(a.out)[(size_t)tok * a.ldo + col] = from_f32<O>(silu_mul_bf16(g, up));
+                reinterpret_cast<O*>(a.out)[(size_t)tok * a.ldo + col] =
+                    from_f32<O>(a.pointwise == 1 ? clamped_swish_mul_bf16(g, up, a.p0, a.p1) : silu_mul_bf16(g, up));
             }
         }
     }
@@ -248,6 +250,21 @@ LLME_API int llme_gemm_skinny_swiglu_bf16(const void* x, long long ldx, const vo
     if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
     if (ldo < inter) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");
     SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, 2 * inter, K, inter, 0, 0.0f, 0.0f};
+    if (out_dtype == LLME_F32) return dispatch<float>(a, stream);
+    if (out_dtype == LLME_BF16) return dispatch<bf16>(a, stream);
+    LLME_REFUSE("gemm_skinny: unsupported output dtype %d", out_dtype);
+}
+
+// out[M, inter] = act(x Wg^T, x Wu^T) with W = [Wg | Wu]: act 0 = silu(g) u; act 1 = the clamped gate, p0 = limit, p1 = slope.
+LLME_API int llme_gemm_skinny_gated_bf16(const void* x, long long ldx, const void* w, long long ldw, void* out, int out_dtype,
+                                         long long ldo, int M, int inter, int K, int act, float p0, float p1, cudaStream_t stream) {
+    if (M <= 0 || inter <= 0) return 0;
+    if (!x || !w || !out) LLME_REFUSE("gemm_skinny: null pointer");
+    if (act != 0 && act != 1) LLME_REFUSE("gemm_skinny: unknown gated activation %d", act);
+    if (inter > (1 << 29) || !llme_gemm_skinny_supports(M, 2 * inter, K, ldx, ldw)) LLME_REFUSE("gemm_skinny: M=%d inter=%d K=%d ldx=%lld ldw=%lld is not supported (M <= 16, K and strides multiples of 8)", M, inter, K, ldx, ldw);
+    if (((uintptr_t)x | (uintptr_t)w) % 16) LLME_REFUSE("gemm_skinny: operands must be 16-byte aligned");
+    if (ldo < inter) LLME_REFUSE("gemm_skinny: output row stride shorter than the row");
+    SkinnyArgs a{(const bf16*)x, ldx, (const bf16*)w, ldw, out, ldo, M, 2 * inter, K, inter, act, p0, p1};
     if (out_dtype == LLME_F32) return dispatch<float>(a, stream);
     if (out_dtype == LLME_BF16) return dispatch<bf16>(a, stream);
     LLME_REFUSE("gemm_skinny: unsupported output dtype %d", out_dtype);

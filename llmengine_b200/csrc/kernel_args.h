@@ -67,3 +67,54 @@ typedef struct LlmeLatentAttnArgs {
     int max_blocks, tokens, nh, rank, rot, page_size;
     float scale;
 } LlmeLatentAttnArgs;
+
+/* Whole-projection norm, partial rotation and cache write for an attention whose keys and values differ in width
+ * (csrc/attention_window.cu).  A cache page holds [nkv][page_size][dk] keys, then [nkv][page_size][dv] values. */
+typedef struct LlmeWindowPostArgs {
+    const void* q_in; const void* k_in; const void* v_in;   /* k_in / v_in NULL: nothing is stored */
+    long long q_stride, k_stride, v_stride;
+    const float* q_gain; const float* k_gain; float eps;     /* gains NULL: no norm; [nh * dk], [nkv * dk] */
+    const float* inv_freq; int rot_dims; float amplitude;    /* inv_freq NULL: no rotation */
+    const int* positions;
+    void* q_out;                                             /* [T, nh * dk] */
+    void* cache; const int* slot_mapping;
+    int tokens, nh, nkv, dk, dv, page_size;
+} LlmeWindowPostArgs;
+
+/* Attention over such a cache: query i sees key j if j <= i and (i - j < window or j < keep_first). */
+typedef struct LlmeWindowAttnArgs {
+    const void* q; const void* cache; void* out;             /* q [T, nh * dk]; out [T, nh * dv] */
+    const float* sink;                                       /* [nh] or NULL */
+    const int* positions; const int* token_request; const int* block_tables;
+    int max_blocks, tokens, nh, nkv, dk, dv, page_size, window, keep_first;
+    float scale;
+} LlmeWindowAttnArgs;
+
+/* The same for the tensor-core kernel: the requests `rows` of the batch, each with its tokens
+ * cu_q_lens[row] .. cu_q_lens[row + 1] that end at position ctx_lens[row] - 1. */
+typedef struct LlmeWindowFastArgs {
+    const void* q; const void* cache; void* out;
+    const float* sink;
+    const int* rows; const int* cu_q_lens; const int* ctx_lens; const int* table_rows; const int* block_tables;
+    int max_blocks, n_rows, nh, nkv, page_size, window, keep_first;
+    float scale;
+} LlmeWindowFastArgs;
+
+/* Routing of a mixture of experts (csrc/moe.cu). */
+typedef struct LlmeMoeRouteArgs {
+    const float* logits; long long ld;                       /* [T, E] */
+    int tokens, num_experts, top_k; float scale;
+    int* experts; float* weights;                            /* [T, top_k] */
+    int* offsets; int* order; int* counts;                   /* [E + 1], [T * top_k], [E] (zero between launches) */
+} LlmeMoeRouteArgs;
+
+/* One product per expert over the rows routed to it. */
+typedef struct LlmeGroupedArgs {
+    const void* x; long long ldx;
+    const void* w; long long ldw, w_expert;                  /* [E, n, k] */
+    void* out; long long ldo;
+    const int* offsets; const int* order;
+    int pairs, num_experts, top_k, n, k;                     /* pairs = tokens * top_k */
+    int gather, scatter;                                     /* x row = order[r] / top_k; out row = order[r] */
+    int act;                                                 /* 1: w[e] = [gate | up], the row written is silu(gate) * up, n / 2 wide */
+} LlmeGroupedArgs;

@@ -249,3 +249,88 @@ LLME_API int llme_latent_post(const LlmeLatentPostArgs* args, int dtype, cudaStr
 #undef LLME_LP
     LLME_LAUNCH_STATUS();
 }
+
+// ----------------------------------------------------------------------------- the norm on a sublayer's output
+// accumulate: x += y / sqrt(mean(y^2) + eps) * gain; else x = ... (y may be x itself: a value is read and written by
+// the same thread, after the sum of squares is complete).  Without y nothing is added.  `copy`, if given, receives the
+// new x in its own type: the next sublayer's products read it.
+template <typename Y, typename G, typename C>
+__global__ void postnorm_kernel(float* x, const Y* y, const G* __restrict__ gain, C* __restrict__ copy, int cols, float eps,
+                                int accumulate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * cols;
+    float rinv = 0.0f;
+    if (y) {
+        float ss = 0.0f;
+        for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+            const float v = to_f32(y[base + j]);
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        rinv = 1.0f / sqrtf(ss / (float)cols + eps);
+    }
+    for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+        float v = accumulate || !y ? x[base + j] : 0.0f;
+        if (y) {
+            v += (to_f32(y[base + j]) * rinv) * to_f32(gain[j]);
+            x[base + j] = v;
+        }
+        if (copy) copy[base + j] = from_f32<C>(v);
+    }
+}
+
+LLME_API int llme_postnorm(float* x, const void* y, int y_dtype, const void* gain, int gain_dtype, void* copy, int copy_dtype,
+                           int rows, int cols, float eps, int accumulate, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!x || (y && !gain) || (!y && !copy)) LLME_REFUSE("postnorm: null pointer");
+    if (y && !(eps > 0.0f)) LLME_REFUSE("postnorm: eps must be positive");
+    if (copy && copy_dtype != LLME_BF16 && copy_dtype != LLME_F32) LLME_REFUSE("postnorm: unsupported copy dtype %d", copy_dtype);
+    const int threads = cols >= 4096 ? 1024 : (cols >= 2048 ? 512 : (cols >= 1024 ? 256 : 128));
+#define LLME_PN(Y, G, C) llme_launch(postnorm_kernel<Y, G, C>, dim3(rows), dim3(threads), 0, stream, x, (const Y*)y, (const G*)gain, (C*)copy, cols, eps, accumulate)
+#define LLME_PN_C(Y, G) do { if (copy && copy_dtype == LLME_F32) LLME_PN(Y, G, float); else LLME_PN(Y, G, __nv_bfloat16); } while (0)
+    if (!y) LLME_PN_C(float, float);
+    else if (y_dtype == LLME_F32 && gain_dtype == LLME_F32) LLME_PN_C(float, float);
+    else if (y_dtype == LLME_F32 && gain_dtype == LLME_BF16) LLME_PN_C(float, __nv_bfloat16);
+    else if (y_dtype == LLME_BF16 && gain_dtype == LLME_F32) LLME_PN_C(__nv_bfloat16, float);
+    else if (y_dtype == LLME_BF16 && gain_dtype == LLME_BF16) LLME_PN_C(__nv_bfloat16, __nv_bfloat16);
+    else LLME_REFUSE("postnorm: unsupported dtypes %d / %d", y_dtype, gain_dtype);
+#undef LLME_PN_C
+#undef LLME_PN
+    LLME_LAUNCH_STATUS();
+}
+
+// ----------------------------------------------------------------------------- out = act(gate, up), gate_up = [gate | up] by columns
+// act 0: g sigmoid(g) u.  act 1 (p0 = limit, p1 = slope): g' = min(g, limit), u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).
+__device__ __forceinline__ float gated_activation(int act, float g, float u, float p0, float p1) {
+    if (act == 1) {
+        g = fminf(g, p0);
+        u = fminf(fmaxf(u, -p0), p0);
+        return (g * sigmoid(p1 * g)) * (u + 1.0f);
+    }
+    return (g * sigmoid(g)) * u;
+}
+
+template <typename T>
+__global__ void gated_act_kernel(const T* __restrict__ gate_up, long long ld_in, T* __restrict__ out, long long ld_out, int cols, int act, float p0,
+                                 float p1) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const T* i = gate_up + (size_t)blockIdx.x * ld_in;
+    T* o = out + (size_t)blockIdx.x * ld_out;
+    for (int j = blockIdx.y * blockDim.x + threadIdx.x; j < cols; j += gridDim.y * blockDim.x)
+        o[j] = from_f32<T>(gated_activation(act, to_f32(i[j]), to_f32(i[cols + j]), p0, p1));
+}
+
+LLME_API int llme_gated_act(const void* gate_up, long long ld_in, void* out, long long ld_out, int dtype, int rows, int cols, int act,
+                            float p0, float p1, cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return 0;
+    if (!gate_up || !out) LLME_REFUSE("gated_act: null pointer");
+    if (act != 0 && act != 1) LLME_REFUSE("gated_act: unknown activation %d", act);
+    const int threads = 128;
+    if (dtype == LLME_F32) llme_launch(gated_act_kernel<float>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const float*)gate_up, ld_in, (float*)out, ld_out, cols, act, p0, p1);
+    else if (dtype == LLME_BF16) llme_launch(gated_act_kernel<__nv_bfloat16>, grid_for(rows, cols, threads), dim3(threads), 0, stream, (const __nv_bfloat16*)gate_up, ld_in, (__nv_bfloat16*)out, ld_out, cols, act, p0, p1);
+    else LLME_REFUSE("gated_act: unsupported dtype %d", dtype);
+    LLME_LAUNCH_STATUS();
+}

@@ -32,6 +32,19 @@ class Op:
 class Plan:
     def __init__(self) -> None:
         self.ops: List[Op] = []
+        self._copies: Dict[int, torch.Tensor] = {}     # address of a 32-bit tensor -> its present copy in the product type
+
+    # A part whose sublayers read the residual stream itself needs it in the type of the matrix products.  The record
+    # that last changed the stream may have written that copy in the same pass; it says so here, and a record that
+    # changes the stream without doing so withdraws it.
+    def note_copy(self, x: torch.Tensor, copy: Optional[torch.Tensor]) -> None:
+        if copy is None:
+            self._copies.pop(x.data_ptr(), None)
+        else:
+            self._copies[x.data_ptr()] = copy
+
+    def copy_of(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        return self._copies.get(x.data_ptr())
 
     def _add(self, kind: str, **a: Any) -> None:
         self.ops.append(Op(kind, a))
@@ -45,15 +58,21 @@ class Plan:
         """x += delta (if given), out = rmsnorm(x) * gain; `rows` = "logits": only the step's wanted rows,
         gathered into the first rows of `out`."""
         self._add("rmsnorm", x=x, gain=gain, eps=float(eps), out=out, delta=delta, rows=rows)
+        if delta is not None:
+            self.note_copy(x, None)
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], rows: str = ROWS_TOKENS) -> None:
         """out = x w^T for the step's tokens (or its wanted rows); `out` None: the step's logits."""
         self._add("linear", x=x, w=w, out=out, rows=rows)
 
-    def linear_swiglu(self, x: torch.Tensor, w_gate_up: torch.Tensor, gate_up: torch.Tensor, out: torch.Tensor) -> None:
-        """out = silu(x Wg^T) * (x Wu^T) with w_gate_up = [Wg | Wu] by rows; `gate_up` is the workspace of the form
-        that runs the product and the activation as two kernels."""
-        self._add("linear_swiglu", x=x, w_gate_up=w_gate_up, gate_up=gate_up, out=out)
+    def linear_swiglu(self, x: torch.Tensor, w_gate_up: torch.Tensor, gate_up: torch.Tensor, out: torch.Tensor,
+                      act: str = "silu", params: tuple = ()) -> None:
+        """out = act(x Wg^T, x Wu^T) with w_gate_up = [Wg | Wu] by rows; `gate_up` is the workspace of the form
+        that runs the product and the activation as two kernels.  Gated activations of (g, u):
+        "silu": g sigmoid(g) u;  "clamped_swish" with params (limit, slope): g' = min(g, limit),
+        u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1)."""
+        self._add("linear_swiglu", x=x, w_gate_up=w_gate_up, gate_up=gate_up, out=out, act=act,
+                  params=tuple(float(p) for p in params))
 
     def qkv_post(self, *, q_in, k_in, v_in, num_heads: int, num_kv_heads: int, head_dim: int, q_gain=None, k_gain=None,
                  eps: float = 0.0, cos_sin=None, q_out=None, k_out=None, cache=None, group: int = 0) -> None:
@@ -98,6 +117,7 @@ class Plan:
     def residual_add(self, x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None) -> None:
         """x += a (+ b) in 32-bit: contributions that no following norm adds."""
         self._add("residual_add", x=x, a=a, b=b)
+        self.note_copy(x, None)
 
     def latent_attention(self, *, q_rot, kv_in, c_gain, eps: float, inv_freq, rot_dims: int, q, out, cache, group: int,
                          num_heads: int, kv_rank: int, rot_dim: int, scale: float, sink=None, scratch=None) -> None:
@@ -118,3 +138,52 @@ class Plan:
         the form that runs this as single kernels."""
         self._add("token_side", x=x, a=a, b=b, table=table, offset=int(offset), dim=int(dim), w_gate=w_gate, w_proj=w_proj,
                   gain=gain, eps=float(eps), xb=xb, g=g, y=y)
+        self.note_copy(x, None)
+
+    def postnorm(self, x: torch.Tensor, y: Optional[torch.Tensor], gain: Optional[torch.Tensor], eps: float,
+                 accumulate: bool = True, copy: Optional[torch.Tensor] = None) -> None:
+        """The norm on a sublayer's output: x += y / sqrt(mean(y^2) + eps) * gain in 32-bit (`accumulate` False:
+        x = ...; y may then be x itself), and `copy`, if given, receives the new x in its own type.  Without y only
+        the copy is made."""
+        self._add("postnorm", x=x, y=y, gain=gain, eps=float(eps), accumulate=bool(accumulate), copy=copy)
+        self.note_copy(x, copy)
+
+    def window_attention(self, *, q_in, k_in, v_in, q_gain, k_gain, eps: float, inv_freq, rot_dims: int, amplitude: float,
+                         q, out, cache, group: int, num_heads: int, num_kv_heads: int, qk_dim: int, v_dim: int,
+                         window: int, keep_first: int, scale: float, sink=None) -> None:
+        """Grouped-query attention over a cache whose keys are `qk_dim` and whose values are `v_dim` wide, from the raw
+        projections: q_in [T, H qk_dim] and, for a layer that stores, k_in [T, G qk_dim] and v_in [T, G v_dim] (column
+        ranges of one product).  With gains, queries and keys are RMS-normed over the WHOLE projection (all heads at
+        once, gain vectors of that size); the first `rot_dims` coordinates of every head are rotated in rotate-half
+        pairs by position * inv_freq[i], cosine and sine times `amplitude` (inv_freq None: no rotation); keys and
+        values are stored.  Then query i sees key j if j <= i and (i - j < window or j < keep_first) (window 0: every
+        earlier key); score = q . k * scale; softmax whose denominator also holds exp(sink_h) when `sink` [H] is given;
+        out [T, H v_dim].  `q` [T, H qk_dim] is the workspace of the finished queries."""
+        self._add("window_attention", q_in=q_in, k_in=k_in, v_in=v_in, q_gain=q_gain, k_gain=k_gain, eps=float(eps),
+                  inv_freq=inv_freq, rot_dims=int(rot_dims), amplitude=float(amplitude), q=q, out=out, cache=cache, group=group,
+                  num_heads=num_heads, num_kv_heads=num_kv_heads, qk_dim=qk_dim, v_dim=v_dim, window=int(window),
+                  keep_first=int(keep_first), scale=float(scale), sink=sink)
+
+    def moe_route(self, *, logits, top_k: int, scale: float, experts, weights, offsets, order, counts) -> None:
+        """Routing of every token of the step from its router `logits` [T, E] (32-bit): scores = sigmoid(logits); the
+        `top_k` largest are chosen (`experts` [T, top_k] int32, best first) with `weights` [T, top_k] = their scores
+        divided by their sum (+ 1e-20) times `scale`.  The (token, choice) pairs are then listed expert by expert:
+        `offsets` [E + 1] int32 with the pairs of expert e at order[offsets[e] : offsets[e + 1]], a pair being
+        token * top_k + choice.  `counts` [E] int32 is scratch that is zero between launches."""
+        self._add("moe_route", logits=logits, top_k=int(top_k), scale=float(scale), experts=experts, weights=weights,
+                  offsets=offsets, order=order, counts=counts)
+
+    def grouped_linear(self, *, x, w, out, offsets, order, top_k: int, gather: bool, scatter: bool, mid=None,
+                       act: Optional[str] = None) -> None:
+        """One product per expert over the rows that were routed to it: for place r of expert e's range of `order`,
+        out_row = w[e] x_row, with x_row = x[order[r] // top_k] if `gather` (the token's row) else x[r], and written
+        to out[order[r]] if `scatter` (the pair's row) else out[r].  w is [E, n, k].  With `act` ("silu"), w[e] is
+        [gate | up] by rows and the row written is silu(gate) * up, half as wide (`mid` [pairs, n]: workspace of the
+        form that runs product and activation apart)."""
+        self._add("grouped_linear", x=x, w=w, out=out, offsets=offsets, order=order, top_k=int(top_k), gather=bool(gather),
+                  scatter=bool(scatter), mid=mid, act=act)
+
+    def moe_combine(self, *, y, weights, base, out) -> None:
+        """out[t] = base[t] (if given) + sum_k weights[t, k] * y[t * top_k + k], the choices added in their order,
+        in 32-bit."""
+        self._add("moe_combine", y=y, weights=weights, base=base, out=out)

@@ -68,10 +68,14 @@ typedef int (*LlmeCallFn)(void* user, const LlmeStep* step, cudaStream_t stream)
 enum LlmeOpKind {
     LLME_OP_EMBEDDING = 1, LLME_OP_RMSNORM, LLME_OP_LINEAR, LLME_OP_LINEAR_SWIGLU, LLME_OP_QKV_POST, LLME_OP_ATTEND,
     LLME_OP_ATTENTION, LLME_OP_CALL, LLME_OP_LINEAR_ACT, LLME_OP_POINTWISE, LLME_OP_BATCHED_LINEAR, LLME_OP_RESIDUAL_ADD,
-    LLME_OP_LATENT_ATTENTION, LLME_OP_TOKEN_SIDE
+    LLME_OP_LATENT_ATTENTION, LLME_OP_TOKEN_SIDE, LLME_OP_POSTNORM, LLME_OP_WINDOW_ATTENTION, LLME_OP_MOE_ROUTE,
+    LLME_OP_GROUPED_LINEAR, LLME_OP_MOE_COMBINE
 };
 
 enum { LLME_ACT_XIELU = 1 };
+/* activations of a (gate, up) pair: g sigmoid(g) u; with p0 = limit, p1 = slope: g' = min(g, limit),
+ * u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1) */
+enum { LLME_GATE_SILU = 0, LLME_GATE_CLAMPED_SWISH = 1 };
 enum { LLME_POINTWISE_SIGMOID_MUL = 1 };
 
 enum { LLME_ROWS_TOKENS = 0, LLME_ROWS_LOGITS = 1 };
@@ -104,6 +108,7 @@ typedef struct LlmeLinearSwigluOp {
     void* gate_up;             /* [T, 2 * inter] workspace for the unfused form */
     void* out; long long ldo;  /* [T, inter] */
     int inter, k;
+    int act; float p0, p1;     /* LLME_GATE_* and its constants */
 } LlmeLinearSwigluOp;
 
 /* QK norm, rotation and cache write as a step of its own (the parts of it that are given). */
@@ -187,6 +192,51 @@ typedef struct LlmeTokenSideOp {
     void* xb; void* g; int act_dtype; float* y;               /* workspace: [T, size], [T, dim], [T, size] */
 } LlmeTokenSideOp;
 
+/* The norm on a sublayer's output: x += y / sqrt(mean(y^2) + eps) * gain (accumulate 0: x = ...; y may be x), and the
+ * new x written to `copy` in its type; y NULL: only the copy. */
+typedef struct LlmePostNormOp {
+    float* x; const void* y; int y_dtype;
+    const void* gain; int gain_dtype; float eps;
+    void* copy; int copy_dtype;
+    int size, accumulate;
+} LlmePostNormOp;
+
+/* Grouped-query attention with keys dk and values dv wide, from the raw projections: norm of q and k over the whole
+ * projection, rotation of the first rot_dims coordinates of every head, cache write, then attention in which query i
+ * sees key j if j <= i and (i - j < window or j < keep_first), with an optional sink per head in the denominator
+ * (csrc/attention_window.cu; a cache page holds [nkv][page][dk] keys, then [nkv][page][dv] values). */
+typedef struct LlmeWindowAttentionOp {
+    const void* q_in; const void* k_in; const void* v_in; long long q_stride, k_stride, v_stride; int dtype;
+    const float* q_gain; const float* k_gain; float eps;
+    const float* inv_freq; int rot_dims; float amplitude;
+    void* q; void* out;                                       /* [T, nh dk] workspace; [T, nh dv] */
+    void* cache; int group;
+    int nh, nkv, dk, dv, window, keep_first; float scale;
+    const float* sink;
+} LlmeWindowAttentionOp;
+
+/* Routing of a mixture of experts: sigmoid scores, the top_k largest, weights = chosen scores / their sum * scale;
+ * the (token, choice) pairs listed expert by expert (csrc/moe.cu). */
+typedef struct LlmeMoeRouteOp {
+    const float* logits; long long ld; int num_experts, top_k; float scale;
+    int* experts; float* weights; int* offsets; int* order; int* counts;
+} LlmeMoeRouteOp;
+
+/* One product per expert over the pairs routed to it. */
+typedef struct LlmeGroupedLinearOp {
+    const void* x; long long ldx; int x_dtype;
+    const void* w; long long ldw, w_expert; int w_dtype;      /* [E, n, k] */
+    void* out; long long ldo; int out_dtype;
+    void* mid; long long ld_mid;                              /* [pairs, n]: workspace of the unfused activation, or NULL */
+    const int* offsets; const int* order;
+    int num_experts, top_k, n, k, gather, scatter, act;       /* act 1: w[e] = [gate | up], out = silu(gate) * up */
+} LlmeGroupedLinearOp;
+
+/* out[t] = base[t] + sum_k weights[t, k] y[t top_k + k]. */
+typedef struct LlmeMoeCombineOp {
+    const float* y; long long ldy; const float* weights; const float* base; float* out; int top_k, size;
+} LlmeMoeCombineOp;
+
 typedef struct LlmeExecutor LlmeExecutor;
 typedef struct LlmePlan LlmePlan;
 
@@ -196,7 +246,9 @@ void llme_executor_destroy(LlmeExecutor*);
  * "gemm_skinny", "gemm_skinny_swiglu", "gemm_tc", "gemm_tc_swiglu", "attention_plain", and per head size
  * "attention_portion/<hd>", "attention_decode/<hd>", "attention_decode_fused/<hd>", "attention_tc/<hd>"; "xielu",
  * "sigmoid_mul", "residual_add", "gelu_gather_mul", "rmsnorm_add", "latent_post", "gemm_f32_batched",
- * "latent_attention_plain", and per latent size "latent_attention_tc/<rank>", "latent_attention_tc_fits/<rank>". */
+ * "latent_attention_plain", and per latent size "latent_attention_tc/<rank>", "latent_attention_tc_fits/<rank>";
+ * "postnorm", "gated_act", "gemm_skinny_gated", "gemm_tc_gated", "window_post", "window_attention_plain", per pair of
+ * key and value sizes "window_attention_tc/<dk>x<dv>", "moe_route", "grouped_linear", "grouped_linear_tc", "moe_combine". */
 int llme_executor_register(LlmeExecutor*, const char* name, void* entry_point);
 /* Which implementation an operation takes.  Operations and their variants:
  *   "linear":            "auto" | "tcgen05" | "cublas" | "plain"   (bfloat16 products of 128 tokens or more / all)
@@ -276,6 +328,11 @@ public:
     int add(const LlmeResidualAddOp& r) { return add(LLME_OP_RESIDUAL_ADD, &r, sizeof r); }
     int add(const LlmeLatentAttentionOp& r) { return add(LLME_OP_LATENT_ATTENTION, &r, sizeof r); }
     int add(const LlmeTokenSideOp& r) { return add(LLME_OP_TOKEN_SIDE, &r, sizeof r); }
+    int add(const LlmePostNormOp& r) { return add(LLME_OP_POSTNORM, &r, sizeof r); }
+    int add(const LlmeWindowAttentionOp& r) { return add(LLME_OP_WINDOW_ATTENTION, &r, sizeof r); }
+    int add(const LlmeMoeRouteOp& r) { return add(LLME_OP_MOE_ROUTE, &r, sizeof r); }
+    int add(const LlmeGroupedLinearOp& r) { return add(LLME_OP_GROUPED_LINEAR, &r, sizeof r); }
+    int add(const LlmeMoeCombineOp& r) { return add(LLME_OP_MOE_COMBINE, &r, sizeof r); }
     /* One step through the whole plan; throws with the failing record's message. */
     void run(const LlmeStep& step, cudaStream_t stream) {
         if (llme_plan_run(h_, &step, 0, -1, stream)) throw std::runtime_error(ex_.error());

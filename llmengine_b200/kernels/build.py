@@ -32,6 +32,13 @@ SOURCES: Dict[str, str] = {
     "attention_latent": "attention_latent.cu",
     # the same on the tensor cores, per latent size (a multiple of 64): "attention_latent_tc@RANK=512"
     "attention_latent_tc": "attention_latent_tc.cu",
+    # attention with keys and values of different widths, a window that keeps the first positions, and a sink
+    "attention_window": "attention_window.cu",
+    # the same on the tensor cores, per pair of sizes: "attention_window_tc@DK=64,DV=64"
+    "attention_window_tc": "attention_window_tc.cu",
+    # mixture of experts: routing, the grouped product (plain form), the weighted sum; and the grouped product on tensor cores
+    "moe": "moe.cu",
+    "moe_tc": "moe_tc.cu",
     "gemm_f32": "gemm_f32.cu",
     "sampling": "sampling.cu",
     "gemm_skinny": "gemm_skinny.cu",
@@ -58,6 +65,7 @@ VARIANTS: Dict[str, List[str]] = {
     "attention_decode_static": ["attention_decode_static@HEAD_DIM=128"],
     "attention_tc": ["attention_tc@HEAD_DIM=64", "attention_tc@HEAD_DIM=128"],
     "attention_latent_tc": ["attention_latent_tc@RANK=128", "attention_latent_tc@RANK=512"],
+    "attention_window_tc": ["attention_window_tc@DK=64,DV=64", "attention_window_tc@DK=128,DV=128"],
 }
 
 INCLUDE = os.path.join(os.path.dirname(_HERE), "include")
@@ -101,6 +109,10 @@ def build_dir() -> str:
         d = os.path.join(tempfile.gettempdir(), f"llmengine_b200_build_{os.getuid()}")
         os.makedirs(d, exist_ok=True)
         return d
+
+
+def has_source(name: str) -> bool:
+    return name in SOURCES and os.path.isfile(os.path.join(CSRC, SOURCES[name]))
 
 
 def split_key(key: str):
@@ -190,9 +202,10 @@ def ensure_built(names: Iterable[str], extra_flags: Optional[List[str]] = None) 
 
 
 def all_keys() -> List[str]:
-    keys = [n for n in SOURCES if n not in VARIANTS]
-    for v in VARIANTS.values():
-        keys.extend(v)
+    keys = [n for n in SOURCES if n not in VARIANTS and has_source(n)]
+    for n, v in VARIANTS.items():
+        if has_source(n):
+            keys.extend(v)
     return keys
 
 

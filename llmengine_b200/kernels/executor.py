@@ -12,7 +12,9 @@ MAX_GROUPS = 8
 F32, BF16 = 0, 1
 ROWS = {"tokens": 0, "logits": 1}
 (OP_EMBEDDING, OP_RMSNORM, OP_LINEAR, OP_LINEAR_SWIGLU, OP_QKV_POST, OP_ATTEND, OP_ATTENTION, OP_CALL, OP_LINEAR_ACT,
- OP_POINTWISE, OP_BATCHED_LINEAR, OP_RESIDUAL_ADD, OP_LATENT_ATTENTION, OP_TOKEN_SIDE) = range(1, 15)
+ OP_POINTWISE, OP_BATCHED_LINEAR, OP_RESIDUAL_ADD, OP_LATENT_ATTENTION, OP_TOKEN_SIDE, OP_POSTNORM, OP_WINDOW_ATTENTION,
+ OP_MOE_ROUTE, OP_GROUPED_LINEAR, OP_MOE_COMBINE) = range(1, 20)
+GATES = {"silu": 0, "clamped_swish": 1}
 ACTIVATIONS = {"xielu": 1}
 POINTWISE = {"sigmoid_mul": 1}
 
@@ -65,7 +67,8 @@ class LinearOp(Structure):
 
 class LinearSwigluOp(Structure):
     _fields_ = [("x", c_void_p), ("ldx", c_longlong), ("dtype", c_int), ("w_gate_up", c_void_p), ("ldw", c_longlong),
-                ("gate_up", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("inter", c_int), ("k", c_int)]
+                ("gate_up", c_void_p), ("out", c_void_p), ("ldo", c_longlong), ("inter", c_int), ("k", c_int),
+                ("act", c_int), ("p0", c_float), ("p1", c_float)]
 
 
 class QkvPostOp(Structure):
@@ -122,6 +125,36 @@ class TokenSideOp(Structure):
                 ("table", c_void_p), ("table_dtype", c_int), ("ld_table", c_longlong), ("offset", c_int), ("dim", c_int),
                 ("vocab", c_int), ("w_gate", c_void_p), ("w_proj", c_void_p), ("w_dtype", c_int), ("gain", c_void_p),
                 ("gain_dtype", c_int), ("eps", c_float), ("xb", c_void_p), ("g", c_void_p), ("act_dtype", c_int), ("y", c_void_p)]
+
+
+class PostNormOp(Structure):
+    _fields_ = [("x", c_void_p), ("y", c_void_p), ("y_dtype", c_int), ("gain", c_void_p), ("gain_dtype", c_int), ("eps", c_float),
+                ("copy", c_void_p), ("copy_dtype", c_int), ("size", c_int), ("accumulate", c_int)]
+
+
+class WindowAttentionOp(Structure):
+    _fields_ = [("q_in", c_void_p), ("k_in", c_void_p), ("v_in", c_void_p), ("q_stride", c_longlong), ("k_stride", c_longlong),
+                ("v_stride", c_longlong), ("dtype", c_int), ("q_gain", c_void_p), ("k_gain", c_void_p), ("eps", c_float),
+                ("inv_freq", c_void_p), ("rot_dims", c_int), ("amplitude", c_float), ("q", c_void_p), ("out", c_void_p),
+                ("cache", c_void_p), ("group", c_int), ("nh", c_int), ("nkv", c_int), ("dk", c_int), ("dv", c_int),
+                ("window", c_int), ("keep_first", c_int), ("scale", c_float), ("sink", c_void_p)]
+
+
+class MoeRouteOp(Structure):
+    _fields_ = [("logits", c_void_p), ("ld", c_longlong), ("num_experts", c_int), ("top_k", c_int), ("scale", c_float),
+                ("experts", c_void_p), ("weights", c_void_p), ("offsets", c_void_p), ("order", c_void_p), ("counts", c_void_p)]
+
+
+class GroupedLinearOp(Structure):
+    _fields_ = [("x", c_void_p), ("ldx", c_longlong), ("x_dtype", c_int), ("w", c_void_p), ("ldw", c_longlong),
+                ("w_expert", c_longlong), ("w_dtype", c_int), ("out", c_void_p), ("ldo", c_longlong), ("out_dtype", c_int),
+                ("mid", c_void_p), ("ld_mid", c_longlong), ("offsets", c_void_p), ("order", c_void_p), ("num_experts", c_int),
+                ("top_k", c_int), ("n", c_int), ("k", c_int), ("gather", c_int), ("scatter", c_int), ("act", c_int)]
+
+
+class MoeCombineOp(Structure):
+    _fields_ = [("y", c_void_p), ("ldy", c_longlong), ("weights", c_void_p), ("base", c_void_p), ("out", c_void_p),
+                ("top_k", c_int), ("size", c_int)]
 
 
 def declare(lib: ctypes.CDLL) -> None:
@@ -206,8 +239,10 @@ def records(op, keep: List[Any]):
         x, w, gu, out = a["x"], a["w_gate_up"], a["gate_up"], a["out"]
         assert x.dtype == w.dtype == out.dtype and x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
         assert w.shape[0] == 2 * out.shape[1] and w.shape[1] == x.shape[1]
+        p = a.get("params", ())
         return OP_LINEAR_SWIGLU, LinearSwigluOp(x.data_ptr(), x.stride(0), code(x.dtype), w.data_ptr(), w.stride(0), ptr(gu),
-                                                out.data_ptr(), out.stride(0), out.shape[1], x.shape[1])
+                                                out.data_ptr(), out.stride(0), out.shape[1], x.shape[1], GATES[a.get("act", "silu")],
+                                                p[0] if p else 0.0, p[1] if len(p) > 1 else 0.0)
     if k == "qkv_post":
         return OP_QKV_POST, _qkv_post_record(a)
     if k == "attend":
@@ -275,4 +310,47 @@ def records(op, keep: List[Any]):
                                           table.stride(0), a["offset"], dim, table.shape[0], wg.data_ptr(), wp.data_ptr(),
                                           code(wg.dtype), gain.data_ptr(), code(gain.dtype), a["eps"], xb.data_ptr(), g.data_ptr(),
                                           code(g.dtype), y.data_ptr())
+    if k == "postnorm":
+        x, y, g, c = a["x"], a["y"], a["gain"], a["copy"]
+        assert x.dtype == torch.float32 and x.is_contiguous() and (y is None or (y.is_contiguous() and y.shape[1] == x.shape[1]))
+        assert (y is None) == (g is None) and (c is None or (c.is_contiguous() and c.shape[1] == x.shape[1])) and (y is not None or c is not None)
+        return OP_POSTNORM, PostNormOp(x.data_ptr(), ptr(y), code(y.dtype) if y is not None else 0, ptr(g),
+                                       code(g.dtype) if g is not None else 0, a["eps"], ptr(c), code(c.dtype) if c is not None else 0,
+                                       x.shape[1], 1 if a["accumulate"] else 0)
+    if k == "window_attention":
+        qi, ki, vi, q, out, cache = a["q_in"], a["k_in"], a["v_in"], a["q"], a["out"], a["cache"]
+        H, G, dk, dv = a["num_heads"], a["num_kv_heads"], a["qk_dim"], a["v_dim"]
+        assert qi.dtype == q.dtype == out.dtype == cache.dtype and qi.stride(1) == 1 and q.is_contiguous() and out.is_contiguous()
+        assert cache.is_contiguous() and qi.shape[1] == q.shape[1] == H * dk and out.shape[1] == H * dv and cache.shape[1] % (G * (dk + dv)) == 0
+        assert (ki is None) == (vi is None) and (ki is None or (ki.dtype == vi.dtype == qi.dtype and ki.stride(1) == vi.stride(1) == 1
+                                                              and ki.shape[1] == G * dk and vi.shape[1] == G * dv))
+        for t, n in ((a["q_gain"], H * dk), (a["k_gain"], G * dk), (a["sink"], H), (a["inv_freq"], a["rot_dims"] // 2)):
+            assert t is None or (t.dtype == torch.float32 and t.is_contiguous() and t.numel() == n)
+        return OP_WINDOW_ATTENTION, WindowAttentionOp(
+            qi.data_ptr(), ptr(ki), ptr(vi), qi.stride(0), ki.stride(0) if ki is not None else 0, vi.stride(0) if vi is not None else 0,
+            code(qi.dtype), ptr(a["q_gain"]), ptr(a["k_gain"]), a["eps"], ptr(a["inv_freq"]), a["rot_dims"], a["amplitude"],
+            q.data_ptr(), out.data_ptr(), cache.data_ptr(), a["group"], H, G, dk, dv, a["window"], a["keep_first"], a["scale"],
+            ptr(a["sink"]))
+    if k == "moe_route":
+        z, ex_, wt, off, order, counts = a["logits"], a["experts"], a["weights"], a["offsets"], a["order"], a["counts"]
+        assert z.dtype == wt.dtype == torch.float32 and z.stride(1) == 1 and ex_.is_contiguous() and wt.is_contiguous()
+        assert all(t.dtype == torch.int32 and t.is_contiguous() for t in (ex_, off, order, counts))
+        E, top = z.shape[1], a["top_k"]
+        assert ex_.shape[1] == wt.shape[1] == top and off.numel() == E + 1 and counts.numel() == E and order.numel() >= ex_.shape[0] * top
+        return OP_MOE_ROUTE, MoeRouteOp(z.data_ptr(), z.stride(0), E, top, a["scale"], ex_.data_ptr(), wt.data_ptr(), off.data_ptr(),
+                                        order.data_ptr(), counts.data_ptr())
+    if k == "grouped_linear":
+        x, w, out, mid = a["x"], a["w"], a["out"], a["mid"]
+        act = 1 if a["act"] else 0
+        assert a["act"] in (None, "silu") and w.dim() == 3 and w.is_contiguous() and x.stride(1) == 1 and out.stride(1) == 1
+        assert w.shape[2] == x.shape[1] and out.shape[1] == (w.shape[1] // 2 if act else w.shape[1]) and x.dtype == w.dtype
+        return OP_GROUPED_LINEAR, GroupedLinearOp(
+            x.data_ptr(), x.stride(0), code(x.dtype), w.data_ptr(), w.stride(1), w.stride(0), code(w.dtype), out.data_ptr(), out.stride(0),
+            code(out.dtype), ptr(mid), mid.stride(0) if mid is not None else 0, a["offsets"].data_ptr(), a["order"].data_ptr(), w.shape[0],
+            a["top_k"], w.shape[1], w.shape[2], 1 if a["gather"] else 0, 1 if a["scatter"] else 0, act)
+    if k == "moe_combine":
+        y, wt, base, out = a["y"], a["weights"], a["base"], a["out"]
+        assert y.dtype == wt.dtype == out.dtype == torch.float32 and y.stride(1) == 1 and wt.is_contiguous() and out.is_contiguous()
+        assert base is None or (base.dtype == torch.float32 and base.is_contiguous() and base.shape[1] == out.shape[1])
+        return OP_MOE_COMBINE, MoeCombineOp(y.data_ptr(), y.stride(0), wt.data_ptr(), ptr(base), out.data_ptr(), wt.shape[1], out.shape[1])
     raise ValueError(f"the executor has no record for the operation {k!r}")

@@ -182,6 +182,11 @@ class CudaOps:
         ld = ((kv_rank + rot_dim + 63) // 64) * 64 + 8
         return (32 + 128) * ld * 2 + 32 * 72 * 2 + 4096 <= 227 * 1024
 
+    @staticmethod
+    def window_tc_supports(qk_dim: int, v_dim: int, dtype: torch.dtype) -> bool:
+        """Whether the tensor-core window attention is built for this pair of sizes (bfloat16, multiples of 16 up to 256)."""
+        return dtype == torch.bfloat16 and qk_dim % 16 == 0 and v_dim % 16 == 0 and 16 <= qk_dim <= 256 and 16 <= v_dim <= 256
+
     def decode_splits(self, requests: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, max_ctx: int) -> int:
         return int(self._xlib.llme_decode_splits(self._ex, requests, num_heads, num_kv_heads, head_dim, window, max_ctx))
 
@@ -191,14 +196,18 @@ class CudaOps:
         "gemm_f32": {"gemm_f32": "llme_gemm_nt_f32", "gemm_f32_batched": "llme_gemm_nt_f32_batched"},
         "pointwise": {"xielu": "llme_xielu", "sigmoid_mul": "llme_sigmoid_mul", "residual_add": "llme_residual_add",
                       "gelu_gather_mul": "llme_gelu_gather_mul", "rmsnorm_add": "llme_rmsnorm_add",
-                      "latent_post": "llme_latent_post"},
+                      "latent_post": "llme_latent_post", "postnorm": "llme_postnorm", "gated_act": "llme_gated_act"},
+        "attention_window": {"window_post": "llme_window_post", "window_attention_plain": "llme_window_attention_plain"},
+        "attention_window_tc": {"window_attention_tc/{hd}": "llme_window_attention_tc"},
+        "moe": {"moe_route": "llme_moe_route", "grouped_linear": "llme_grouped_linear", "moe_combine": "llme_moe_combine"},
+        "moe_tc": {"grouped_linear_tc": "llme_grouped_linear_tc"},
         "attention_latent": {"latent_attention_plain": "llme_latent_attention_plain"},
         "attention_latent_tc": {"latent_attention_tc/{hd}": "llme_latent_attention_tc",
                                 "latent_attention_tc_fits/{hd}": "llme_latent_attention_tc_fits"},
         "gemm_skinny": {"gemm_skinny": "llme_gemm_skinny_bf16", "gemm_skinny_swiglu": "llme_gemm_skinny_swiglu_bf16",
-                        "gemm_skinny_act": "llme_gemm_skinny_act_bf16"},
+                        "gemm_skinny_act": "llme_gemm_skinny_act_bf16", "gemm_skinny_gated": "llme_gemm_skinny_gated_bf16"},
         "gemm_tcgen05": {"gemm_tc": "llme_gemm_tc_bf16", "gemm_tc_swiglu": "llme_gemm_tc_swiglu_bf16",
-                         "gemm_tc_act": "llme_gemm_tc_act_bf16"},
+                         "gemm_tc_act": "llme_gemm_tc_act_bf16", "gemm_tc_gated": "llme_gemm_tc_gated_bf16"},
         "attention_plain": {"attention_plain": "llme_attention_plain"},
         "attention_fast": {"attention_portion/{hd}": "llme_attention_portion", "attention_decode/{hd}": "llme_attention_decode",
                            "attention_decode_fused/{hd}": "llme_attention_decode_fused",
@@ -210,7 +219,7 @@ class CudaOps:
     def _register(self, key: str, lib: ctypes.CDLL) -> None:
         """Hand a kernel library's entry points (and its error text) to the executor, by name."""
         name, _, rest = key.partition("@")
-        hd = rest.partition("=")[2]
+        hd = "x".join(d.partition("=")[2] for d in rest.split(",")) if rest else ""       # "DK=64,DV=32" -> "64x32"
         for entry, symbol in self._ENTRY_POINTS.get(name, {}).items():
             entry = entry.format(hd=hd)
             fn = ctypes.cast(getattr(lib, symbol), c_void_p)
@@ -230,8 +239,18 @@ class CudaOps:
             a = op.a
             if op.kind in ("embedding", "rmsnorm", "qkv_post", "attention"):
                 want("elementwise")
-            if op.kind in ("linear_act", "pointwise", "residual_add", "latent_attention", "token_side"):
+            if op.kind in ("linear_act", "pointwise", "residual_add", "latent_attention", "token_side", "postnorm"):
                 want("pointwise")
+            if op.kind == "linear_swiglu" and a.get("act", "silu") != "silu":
+                want("pointwise")
+            if op.kind == "window_attention":
+                want("attention_window")
+                if fast_attention and build.has_source("attention_window_tc") and self.window_tc_supports(a["qk_dim"], a["v_dim"], a["q"].dtype):
+                    want(f"attention_window_tc@DK={a['qk_dim']},DV={a['v_dim']}")
+            if op.kind in ("moe_route", "grouped_linear", "moe_combine"):
+                want("moe")
+            if op.kind == "grouped_linear" and a["x"].dtype == torch.bfloat16 and self.chosen("linear") != "plain" and build.has_source("moe_tc"):
+                want("moe_tc")
             if op.kind == "latent_attention":
                 want("attention_latent")
                 if fast_attention and self.latent_tc_supports(a["kv_rank"], a["rot_dim"], a["q"].dtype):

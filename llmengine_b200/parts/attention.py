@@ -9,6 +9,8 @@ import torch
 
 from ..config.spec import PartSpec
 from ..engine.plan import Plan
+from dataclasses import dataclass
+
 from .base import PagedKVSpec, Part, Runtime, WeightSpec, build_part, register_part, run_alone
 
 
@@ -96,6 +98,134 @@ class GQAttention(Part):
             if writes:
                 plan.qkv_post(q_in=None, k_in=k, v_in=qkv[:, qs + kvs:], **common)
             plan.attend(q=q, out=out, window=self.window, scale=self.scale, scratch=scratch, **common)
+        delta = rt.workspace("mixer_out", self.hidden, torch.float32)
+        plan.linear(out, self.w_o, delta)
+        return delta
+
+    def forward(self, h: torch.Tensor, batch, cache) -> torch.Tensor:
+        plan = Plan()
+        delta = self.emit(plan, h, cache)
+        run_alone(self.rt, plan, batch)
+        return delta[: h.shape[0]]
+
+
+@dataclass
+class SplitKVView:
+    """The cache a run of `WindowSinkAttention` works on."""
+
+    kv: torch.Tensor                # [pages, kv_heads * page_size * (k_dim + v_dim)]
+    group: int
+    writes: bool
+
+
+@dataclass(frozen=True)
+class SplitKVSpec:
+    """Keys and values of different widths in pages: a page holds the keys of its tokens, [kv_heads, page_size, k_dim],
+    and behind them the values, [kv_heads, page_size, v_dim].  `window` W > 0: only the last W positions are needed,
+    and beside them the first `keep_first` positions of the request, whose pages are never given back."""
+
+    num_kv_heads: int
+    k_dim: int
+    v_dim: int
+    window: int = 0
+    keep_first: int = 0
+    paged = True
+
+    def allocate(self, count: int, page_size: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        return torch.zeros(count, self.num_kv_heads * page_size * (self.k_dim + self.v_dim), dtype=dtype, device=device)
+
+    def bytes_per_token(self, dtype: torch.dtype) -> int:
+        return self.num_kv_heads * (self.k_dim + self.v_dim) * torch.empty((), dtype=dtype).element_size()
+
+    def view(self, tensor: torch.Tensor, group: Optional[int], writes: bool) -> SplitKVView:
+        return SplitKVView(tensor, group, writes)
+
+
+@register_part("mixer", "gqa_window_sink")
+class WindowSinkAttention(Part):
+    """Grouped-query attention with the options of several recent designs, each a parameter:
+
+    * query/key size `qk_dim` and value size `v_dim` per head may differ;
+    * with `norm_eps`, q and k are RMS-normed over the whole projection (all heads at once) with gain vectors of that
+      size, before the rotation;
+    * `position_encoding`: a part that offers `frequencies()`, `dims` and `amplitude` (rotate-half pairs over the first
+      `dims` coordinates of every head), or None;
+    * scores are scaled by `scale`;
+    * query i sees key j if j <= i and (i - j < window or j < keep_first); window 0: every earlier key;
+    * with `sink`, a learned number per head whose exponential joins the softmax denominator (it has no key, no value
+      and is not scaled);
+    * `own_kv` False: the layer has no key and value projections and reads the cache of the run that the layer order
+      names (keys as stored there, normed and rotated); `retain_window` / `retain_first` then say what that cache
+      keeps (the widest needs among the layers that read it), which may be more than this layer's own mask.
+
+    Tensors: q, k, v, o; q.norm, k.norm; sink."""
+
+    def __init__(self, rt: Runtime, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, qk_dim: int,
+                 v_dim: int, scale: float, norm_eps: Optional[float] = None, position_encoding: Optional[PartSpec] = None,
+                 window: int = 0, keep_first: int = 0, sink: bool = False, own_kv: bool = True,
+                 retain_window: Optional[int] = None, retain_first: Optional[int] = None):
+        super().__init__(rt, prefix)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
+        self.hidden, self.nh, self.nkv = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dk, self.dv, self.scale = int(qk_dim), int(v_dim), float(scale)
+        self.eps = None if norm_eps is None else float(norm_eps)
+        self.window, self.keep_first = int(window), int(keep_first)
+        self.retain_window = self.window if retain_window is None else int(retain_window)
+        self.retain_first = self.keep_first if retain_first is None else int(retain_first)
+        if self.retain_window and (not self.window or self.window > self.retain_window or self.keep_first > self.retain_first):
+            raise ValueError(f"{prefix}: the cache keeps less than the layer's mask needs")
+        self.has_sink, self.own_kv = bool(sink), bool(own_kv)
+        self.position = build_part("position", position_encoding, rt, prefix) if position_encoding is not None else None
+        if self.position is not None and self.position.dims > self.dk:
+            raise ValueError(f"{prefix}: {self.position.dims} rotated coordinates do not fit a head of {self.dk}")
+        self.q_size, self.k_size, self.v_size = self.nh * self.dk, self.nkv * self.dk, self.nkv * self.dv
+        self.o_size = self.nh * self.dv
+        self.w_in = self.w_o = self.q_gain = self.k_gain = self.sink = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        s = {self.name("q"): WeightSpec((self.q_size, self.hidden)), self.name("o"): WeightSpec((self.hidden, self.o_size))}
+        if self.own_kv:
+            s[self.name("k")] = WeightSpec((self.k_size, self.hidden))
+            s[self.name("v")] = WeightSpec((self.v_size, self.hidden))
+        if self.eps is not None:
+            s[self.name("q.norm")] = WeightSpec((self.q_size,), role="vector", init="gain")
+            if self.own_kv:
+                s[self.name("k.norm")] = WeightSpec((self.k_size,), role="vector", init="gain")
+        if self.has_sink:
+            s[self.name("sink")] = WeightSpec((self.nh,), role="vector", init="unit")
+        return s
+
+    def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        parts = [t[self.name("q")]] + ([t[self.name("k")], t[self.name("v")]] if self.own_kv else [])
+        self.w_in = torch.cat(parts, dim=0).contiguous()
+        self.w_o = t[self.name("o")].contiguous()
+        if self.eps is not None:
+            self.q_gain = t[self.name("q.norm")].float().contiguous()
+            self.k_gain = t[self.name("k.norm")].float().contiguous() if self.own_kv else None
+        self.sink = t[self.name("sink")].float().contiguous() if self.has_sink else None
+
+    def cache_spec(self) -> SplitKVSpec:
+        return SplitKVSpec(self.nkv, self.dk, self.dv, self.retain_window, self.retain_first)
+
+    def emit(self, plan: Plan, h: torch.Tensor, cache) -> torch.Tensor:
+        rt = self.rt
+        if cache.writes != self.own_kv:
+            raise ValueError(f"{self.prefix}: a layer with key and value projections keeps a cache of its own, one "
+                             f"without reads another layer's")
+        qs, ks = self.q_size, self.k_size
+        proj = rt.workspace("qkv", self.w_in.shape[0], rt.dtype)
+        plan.linear(h, self.w_in, proj)
+        q = rt.workspace("q", qs, rt.dtype)
+        out = rt.workspace("attn_out", self.o_size, rt.dtype)
+        pos = self.position
+        plan.window_attention(
+            q_in=proj[:, :qs], k_in=proj[:, qs:qs + ks] if self.own_kv else None, v_in=proj[:, qs + ks:] if self.own_kv else None,
+            q_gain=self.q_gain, k_gain=self.k_gain, eps=self.eps or 0.0,
+            inv_freq=pos.frequencies() if pos is not None else None, rot_dims=pos.dims if pos is not None else 0,
+            amplitude=pos.amplitude if pos is not None else 1.0, q=q, out=out, cache=cache.kv, group=cache.group,
+            num_heads=self.nh, num_kv_heads=self.nkv, qk_dim=self.dk, v_dim=self.dv, window=self.window,
+            keep_first=self.keep_first, scale=self.scale, sink=self.sink)
         delta = rt.workspace("mixer_out", self.hidden, torch.float32)
         plan.linear(out, self.w_o, delta)
         return delta

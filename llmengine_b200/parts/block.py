@@ -131,3 +131,77 @@ class ParallelResidualBlock(Part):
         x, out = self.emit(plan, x, delta, cache)
         run_alone(self.rt, plan, batch)
         return x, None if out is None else out[: x.shape[0]]
+
+
+@register_part("block", "postnorm_residual")
+class PostNormResidualBlock(Part):
+    """x = x + norm1(mixer(x));  x = x + norm2(feed_forward(x)): the norms stand on the sublayers' OUTPUTS, and the
+    sublayers read the residual stream itself.  A layer may have no feed-forward (and then no second norm).
+
+    The stream is 32-bit.  Where the matrix products take another type, the kernel that adds a normed contribution
+    also writes the new stream in that type, which is what the next sublayer reads.  The block reads the parts
+    "mixer", "mixer_norm" and, where the layer has them, "feed_forward" and "feed_forward_norm" (norm parts with a
+    gain vector and an eps)."""
+
+    def __init__(self, rt: Runtime, prefix: str, layer: LayerSpec, mixer_name: str = "mixer",
+                 feed_forward_name: str = "feed_forward", mixer_norm_name: str = "mixer_norm",
+                 feed_forward_norm_name: str = "feed_forward_norm"):
+        super().__init__(rt, prefix)
+        missing = [n for n in ("mixer", "mixer_norm") if n not in layer.parts]
+        if "feed_forward" in layer.parts and "feed_forward_norm" not in layer.parts:
+            missing.append("feed_forward_norm")
+        if missing:
+            raise ValueError(f"layer {prefix!r}: a postnorm_residual block needs the parts {', '.join(missing)}")
+        self.mixer = build_part("mixer", layer.parts["mixer"], rt, self.name(mixer_name))
+        self.mixer_norm = build_part("norm", layer.parts["mixer_norm"], rt, self.name(mixer_norm_name))
+        has_ffn = "feed_forward" in layer.parts
+        self.ffn = build_part("feed_forward", layer.parts["feed_forward"], rt, self.name(feed_forward_name)) if has_ffn else None
+        self.ffn_norm = build_part("norm", layer.parts["feed_forward_norm"], rt, self.name(feed_forward_norm_name)) if has_ffn else None
+        self.parts = tuple(p for p in (self.mixer, self.mixer_norm, self.ffn, self.ffn_norm) if p is not None)
+        for n in (self.mixer_norm, self.ffn_norm):
+            if n is not None and not (hasattr(n, "gain") and hasattr(n, "eps")):
+                raise ValueError(f"layer {prefix!r}: the norm on a sublayer's output needs a gain vector and an eps")
+        self.capture_safe = all(p.capture_safe and hasattr(p, "emit") for p in (self.mixer, self.ffn) if p is not None)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        out: Dict[str, WeightSpec] = {}
+        for p in self.parts:
+            out.update(p.weight_specs())
+        return out
+
+    def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        for p in self.parts:
+            p.load_weights({n: tensors[n] for n in p.weight_specs()})
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def _input(self, plan: Plan, x: torch.Tensor) -> torch.Tensor:
+        """The stream as a sublayer reads it: itself in the 32-bit engine, else its copy in the product type."""
+        rt = self.rt
+        if rt.dtype == torch.float32:
+            return x
+        h = plan.copy_of(x)
+        if h is None:
+            h = rt.workspace("stream_copy", x.shape[1], rt.dtype)
+            plan.postnorm(x, None, None, 0.0, copy=h)
+        return h
+
+    def emit(self, plan: Plan, x: torch.Tensor, delta: Optional[torch.Tensor], cache):
+        rt = self.rt
+        hidden = x.shape[1]
+        if delta is not None:
+            plan.residual_add(x, delta)
+        copy = None if rt.dtype == torch.float32 else rt.workspace("stream_copy", hidden, rt.dtype)
+        a = emit_mixer(plan, self.mixer, self._input(plan, x), cache, hidden)
+        plan.postnorm(x, a, self.mixer_norm.gain, self.mixer_norm.eps, copy=copy)
+        if self.ffn is not None:
+            b = emit_feed_forward(plan, self.ffn, self._input(plan, x), hidden)
+            plan.postnorm(x, b, self.ffn_norm.gain, self.ffn_norm.eps, copy=copy)
+        return x, None
+
+    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor], batch, cache):
+        plan = Plan()
+        x, _ = self.emit(plan, x, delta, cache)
+        run_alone(self.rt, plan, batch)
+        return x, None

@@ -18,10 +18,16 @@ class TokenEmbedding(Part):
     them as shared tensors and gather from them by the step's token ids."""
 
     def __init__(self, rt: Runtime, prefix: str, vocab_size: int, hidden_size: int, leaf: str = "weight",
-                 extra_tables: Optional[Dict[str, int]] = None):
+                 extra_tables: Optional[Dict[str, int]] = None, norm_leaf: Optional[str] = None,
+                 norm_eps: Optional[float] = None):
         super().__init__(rt, prefix)
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
         self.leaf = leaf
+        # with `norm_leaf`, the gathered rows are RMS-normed with that gain vector before they enter the stream
+        self.norm_leaf, self.norm_eps = norm_leaf, None if norm_eps is None else float(norm_eps)
+        if (norm_leaf is None) != (norm_eps is None):
+            raise ValueError(f"{prefix}: a norm on the embedding needs both its tensor name and its eps")
+        self.norm_gain: Optional[torch.Tensor] = None
         self.extra_widths = {n: int(w) for n, w in dict(extra_tables or {}).items()}
         self.table: Optional[torch.Tensor] = None
         self.extra: Dict[str, torch.Tensor] = {}
@@ -30,11 +36,15 @@ class TokenEmbedding(Part):
         s = {self.name(self.leaf): WeightSpec((self.vocab, self.hidden))}
         for n, w in self.extra_widths.items():
             s[n] = WeightSpec((self.vocab, w), init="unit")
+        if self.norm_leaf is not None:
+            s[self.name(self.norm_leaf)] = WeightSpec((self.hidden,), role="vector", init="gain")
         return s
 
     def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
         self.table = t[self.name(self.leaf)].contiguous()
         self.extra = {n: t[n].contiguous() for n in self.extra_widths}
+        if self.norm_leaf is not None:
+            self.norm_gain = t[self.name(self.norm_leaf)].contiguous()
 
     def shared_tensor(self, name: str) -> Optional[torch.Tensor]:
         if name in self.extra:
@@ -44,6 +54,10 @@ class TokenEmbedding(Part):
     def emit(self, plan: Plan) -> torch.Tensor:
         x = self.rt.workspace("residual", self.hidden, torch.float32)
         plan.embedding(self.table, x)
+        if self.norm_leaf is not None:
+            # the stream in the type of the products too: a block whose sublayers read the stream itself finds it there
+            copy = None if self.rt.dtype == torch.float32 else self.rt.workspace("stream_copy", self.hidden, self.rt.dtype)
+            plan.postnorm(x, x, self.norm_gain, self.norm_eps, accumulate=False, copy=copy)
         return x
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:

@@ -1,7 +1,7 @@
 """Feed-forward parts."""
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
@@ -87,6 +87,124 @@ class DenseXIELU(Part):
         plan.linear_act(h, self.w_up, up, act, "xielu", (self.a_pos, self.a_neg))
         delta = rt.workspace("ffn_out", self.hidden, torch.float32)
         plan.linear(act, self.w_down, delta)
+        return delta
+
+    def forward(self, h: torch.Tensor, batch=None) -> torch.Tensor:
+        from ..engine.batch import StepBatch
+        plan = Plan()
+        delta = self.emit(plan, h)
+        run_alone(self.rt, plan, batch if batch is not None else StepBatch.bare(h.shape[0], h.device))
+        return delta[: h.shape[0]]
+
+
+GATED_ACTIVATIONS = ("silu", "clamped_swish")
+
+
+@register_part("feed_forward", "gated_dense")
+class GatedDense(Part):
+    """down( act(gate(h), up(h)) ), no biases, tensors gate / up / down, the activation a parameter:
+    "silu": g sigmoid(g) u;  "clamped_swish" with `limit` (and `slope`, 1.702 unless given): g' = min(g, limit),
+    u' = clamp(u, -limit, limit), g' sigmoid(slope g') (u' + 1).  The gate and up matrices are stored as one matrix so
+    that one product serves both, with the activation in its epilogue where a kernel has it."""
+
+    def __init__(self, rt: Runtime, prefix: str, hidden_size: int, intermediate_size: int, activation: str = "silu",
+                 limit: Optional[float] = None, slope: float = 1.702):
+        super().__init__(rt, prefix)
+        self.hidden, self.inter = int(hidden_size), int(intermediate_size)
+        if activation not in GATED_ACTIVATIONS:
+            raise ValueError(f"{prefix}: unknown gated activation {activation!r}; known: {', '.join(GATED_ACTIVATIONS)}")
+        if activation == "clamped_swish" and limit is None:
+            raise ValueError(f"{prefix}: the clamped activation needs its limit")
+        self.act = activation
+        self.params = (float(limit), float(slope)) if activation == "clamped_swish" else ()
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {self.name("gate"): WeightSpec((self.inter, self.hidden)), self.name("up"): WeightSpec((self.inter, self.hidden)),
+                self.name("down"): WeightSpec((self.hidden, self.inter))}
+
+    def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        self.w_gate_up = torch.cat([t[self.name("gate")], t[self.name("up")]], 0).contiguous()
+        self.w_down = t[self.name("down")].contiguous()
+
+    def emit(self, plan: Plan, h: torch.Tensor, out_name: str = "ffn_out") -> torch.Tensor:
+        rt = self.rt
+        act = rt.workspace("act", self.inter, rt.dtype)
+        gate_up = rt.workspace("gate_up", 2 * self.inter, rt.dtype)
+        plan.linear_swiglu(h, self.w_gate_up, gate_up, act, act=self.act, params=self.params)
+        delta = rt.workspace(out_name, self.hidden, torch.float32)
+        plan.linear(act, self.w_down, delta)
+        return delta
+
+    def forward(self, h: torch.Tensor, batch=None) -> torch.Tensor:
+        from ..engine.batch import StepBatch
+        plan = Plan()
+        delta = self.emit(plan, h)
+        run_alone(self.rt, plan, batch if batch is not None else StepBatch.bare(h.shape[0], h.device))
+        return delta[: h.shape[0]]
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(Part):
+    """A mixture of `num_experts` small feed-forwards down(silu(gate h) * (up h)) of which every token uses `top_k`:
+    router logits z = W_router h in 32-bit, scores sigmoid(z), the `top_k` largest chosen, weights = the chosen scores
+    divided by their sum (+ 1e-20) times `route_scale`; the output is the weighted sum of the chosen experts' outputs,
+    plus, with `shared_size` > 0, an expert of that size that every token uses.  Tensors: router; e<i>.gate / up /
+    down; shared.gate / up / down.
+
+    The experts' matrices are stacked ([E, 2 ff, D] and [E, D, ff]) and run as two grouped products over the
+    (token, choice) pairs listed expert by expert; the pairs' outputs are combined per token in the order of the
+    choices, so a token's result does not depend on what else is in the step."""
+
+    def __init__(self, rt: Runtime, prefix: str, hidden_size: int, num_experts: int, top_k: int, expert_size: int,
+                 route_scale: float = 1.0, shared_size: int = 0):
+        super().__init__(rt, prefix)
+        self.hidden, self.E, self.top, self.ff = int(hidden_size), int(num_experts), int(top_k), int(expert_size)
+        if not 0 < self.top <= self.E:
+            raise ValueError(f"{prefix}: {self.top} of {self.E} experts cannot be chosen")
+        self.route_scale = float(route_scale)
+        self.shared = (GatedDense(rt, self.name("shared"), hidden_size, int(shared_size)) if shared_size else None)
+        self.w_router = self.w_gate_up = self.w_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        s = {self.name("router"): WeightSpec((self.E, self.hidden))}
+        for e in range(self.E):
+            s[self.name(f"e{e}.gate")] = WeightSpec((self.ff, self.hidden))
+            s[self.name(f"e{e}.up")] = WeightSpec((self.ff, self.hidden))
+            s[self.name(f"e{e}.down")] = WeightSpec((self.hidden, self.ff))
+        if self.shared is not None:
+            s.update(self.shared.weight_specs())
+        return s
+
+    def load_weights(self, t: Dict[str, torch.Tensor]) -> None:
+        self.w_router = t[self.name("router")].contiguous()
+        self.w_gate_up = torch.stack([torch.cat([t[self.name(f"e{e}.gate")], t[self.name(f"e{e}.up")]], 0)
+                                      for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([t[self.name(f"e{e}.down")] for e in range(self.E)]).contiguous()
+        if self.shared is not None:
+            self.shared.load_weights({n: t[n] for n in self.shared.weight_specs()})
+
+    def emit(self, plan: Plan, h: torch.Tensor) -> torch.Tensor:
+        rt = self.rt
+        T, E, top = rt.max_tokens, self.E, self.top
+        logits = rt.workspace("router_logits", E, torch.float32)
+        plan.linear(h, self.w_router, logits)
+        experts = rt.workspace("route_experts", top, torch.int32)
+        weights = rt.workspace("route_weights", top, torch.float32)
+        offsets = rt.buffer("route_offsets", 1, E + 1, torch.int32, exact=True, zero=True).view(-1)
+        counts = rt.buffer("route_counts", 1, E, torch.int32, exact=True, zero=True).view(-1)
+        order = rt.buffer("route_order", T * top, 1, torch.int32).view(-1)
+        plan.moe_route(logits=logits, top_k=top, scale=self.route_scale, experts=experts, weights=weights,
+                       offsets=offsets, order=order, counts=counts)
+        act = rt.buffer("expert_act", T * top, self.ff, rt.dtype)
+        mid = rt.buffer("expert_gate_up", T * top, 2 * self.ff, rt.dtype)
+        plan.grouped_linear(x=h, w=self.w_gate_up, out=act, offsets=offsets, order=order, top_k=top, gather=True,
+                            scatter=False, mid=mid, act="silu")
+        y = rt.buffer("expert_out", T * top, self.hidden, torch.float32)
+        plan.grouped_linear(x=act, w=self.w_down, out=y, offsets=offsets, order=order, top_k=top, gather=False, scatter=True)
+        base = self.shared.emit(plan, h, out_name="shared_out") if self.shared is not None else None
+        delta = rt.workspace("ffn_out", self.hidden, torch.float32)
+        plan.moe_combine(y=y, weights=weights, base=base, out=delta)
         return delta
 
     def forward(self, h: torch.Tensor, batch=None) -> torch.Tensor:

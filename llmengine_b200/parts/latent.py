@@ -49,27 +49,46 @@ class LatentKVSpec:
 @register_part("position", "rotary_partial")
 class PartialRotaryEncoding(Part):
     """Rotate-half rotary encoding of the first `dims` coordinates of a vector; what lies beyond them passes
-    unchanged.  Coordinate i pairs with i + dims/2; at position p the pair is turned by the angle p * base^(-2i/dims).
-    The frequencies are formed once on the host in 32-bit; the kernels form the 32-bit angle and its cosine and
-    sine from the token's position, so there is no table of positions and no longest position."""
+    unchanged.  Coordinate i pairs with i + dims/2; at position p the pair is turned by the angle p * f_i with
+    f_i = base^(-2i/dims).  The frequencies are formed once on the host in 32-bit; the kernels form the 32-bit angle
+    and its cosine and sine from the token's position, so there is no table of positions and no longest position.
+
+    `scaling` = {factor, original, fast, slow} stretches the encoding to sequences `factor` times longer than the
+    `original` length it was made for: with turns(t) = dims ln(original / (2 pi t)) / (2 ln base) the coordinate that
+    makes t turns over the original length, lo = max(floor(turns(fast)), 0), hi = min(ceil(turns(slow)), dims - 1) and
+    r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency becomes f_i / factor * r_i + f_i (1 - r_i) (fast
+    coordinates keep their frequency, slow ones are slowed), and cosine and sine are multiplied by
+    `amplitude` = 0.1 ln(factor) + 1."""
 
     needs_apply = True
 
-    def __init__(self, rt: Runtime, prefix: str, dims: int, base: float):
+    def __init__(self, rt: Runtime, prefix: str, dims: int, base: float, scaling: Optional[dict] = None):
         super().__init__(rt, prefix)
         if dims <= 0 or dims % 2:
             raise ValueError(f"rotary encoding needs an even number of rotated coordinates, got {dims}")
         self.dims, self.base = int(dims), float(base)
+        self.scaling = None if not scaling else tuple(float(scaling[k]) for k in ("factor", "original", "fast", "slow"))
+        self.amplitude = 1.0 if self.scaling is None else float(np.float32(0.1 * np.log(self.scaling[0]) + 1.0))
 
     @staticmethod
-    def build_frequencies(dims: int, base: float) -> torch.Tensor:
+    def build_frequencies(dims: int, base: float, scaling: Optional[tuple] = None) -> torch.Tensor:
         i = np.arange(dims // 2, dtype=np.float32)
         expo = (np.float32(-2.0) * i) / np.float32(dims)
-        return torch.from_numpy(np.power(np.float64(np.float32(base)), expo.astype(np.float64)).astype(np.float32))
+        f = np.power(np.float64(np.float32(base)), expo.astype(np.float64))
+        if scaling is not None:
+            factor, original, fast, slow = scaling
+
+            def turns(t: float) -> float:
+                return dims * np.log(original / (2.0 * np.pi * t)) / (2.0 * np.log(base))
+            lo = max(int(np.floor(turns(fast))), 0)
+            hi = min(int(np.ceil(turns(slow))), dims - 1)
+            ramp = np.clip((i.astype(np.float64) - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / factor * ramp + f * (1.0 - ramp)
+        return torch.from_numpy(f.astype(np.float32))
 
     def frequencies(self) -> torch.Tensor:
-        return self.rt.shared_table(("rotary_partial", self.dims, self.base),
-                                    lambda: self.build_frequencies(self.dims, self.base))
+        return self.rt.shared_table(("rotary_partial", self.dims, self.base, self.scaling),
+                                    lambda: self.build_frequencies(self.dims, self.base, self.scaling))
 
     def rotary_table(self) -> Optional[torch.Tensor]:
         return None

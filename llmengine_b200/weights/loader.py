@@ -73,6 +73,9 @@ def load_model_weights(model, config, model_dir: str, compute: torch.dtype, devi
     ignorable = [n for n in model.tied_tensors() if n in where and n not in specs]
     for n in ignorable:
         print(f"[llmengine_b200] {n} is tied to {model.tied_tensors()[n]}: the file's copy is ignored", file=sys.stderr)
+    extra = getattr(config, "ignorable_tensor", None)      # tensors a file may hold that the model has no use for
+    if extra is not None:
+        ignorable += [n for n in where if n not in specs and extra(n)]
     check_names_and_shapes(specs, {n: f.shape(raw) for n, (f, raw) in where.items()}, ignorable)
     tensors: Dict[str, torch.Tensor] = {}
     for name, spec in specs.items():

@@ -156,6 +156,99 @@ class HostOps:
             w = torch.softmax(s, -1)[:, : p + 1]
             out[t] = (w @ rows[:, :r]).to(out.dtype)
 
+    def gated_act(self, act, params, gate_up, out):
+        assert act == "clamped_swish"
+        limit, slope = params
+        inter = out.shape[1]
+        g = torch.clamp(gate_up[:, :inter].float(), max=limit)
+        u = torch.clamp(gate_up[:, inter:].float(), -limit, limit)
+        out.copy_((g * torch.sigmoid(slope * g) * (u + 1.0)).to(out.dtype))
+
+    def postnorm(self, x, y, gain, eps, accumulate, copy):
+        if y is not None:
+            yf = y.float()
+            n = yf * (1.0 / torch.sqrt((yf * yf).mean(-1, keepdim=True) + eps)) * gain.float()
+            if accumulate:
+                x += n
+            else:
+                x.copy_(n)
+        if copy is not None:
+            copy.copy_(x.to(copy.dtype))
+
+    def window_attention(self, a, T, positions, token_request, block_tables, slot_mapping, page_size):
+        H, G, dk, dv = a["num_heads"], a["num_kv_heads"], a["qk_dim"], a["v_dim"]
+        cache, ps = a["cache"], page_size
+        pages = cache.view(cache.shape[0], -1)
+        keys = pages[:, :G * ps * dk].view(-1, G, ps, dk)
+        vals = pages[:, G * ps * dk:].view(-1, G, ps, dv)
+
+        def finish(x, heads, gain):
+            x = x[:T].float()
+            if gain is not None:
+                x = x * (1.0 / torch.sqrt((x * x).mean(-1, keepdim=True) + a["eps"])) * gain
+            x = x.view(T, heads, dk)
+            if a["inv_freq"] is not None:
+                half = a["rot_dims"] // 2
+                ang = positions.float()[:, None] * a["inv_freq"][None, :]
+                c, s = (torch.cos(ang) * a["amplitude"])[:, None, :], (torch.sin(ang) * a["amplitude"])[:, None, :]
+                u, v = x[..., :half], x[..., half:2 * half]
+                x = torch.cat([u * c - v * s, v * c + u * s, x[..., 2 * half:]], -1)
+            return x
+        q = finish(a["q_in"], H, a["q_gain"]).to(cache.dtype)
+        a["q"][:T] = q.reshape(T, -1)
+        if a["k_in"] is not None:
+            k = finish(a["k_in"], G, a["k_gain"]).to(cache.dtype)
+            v = a["v_in"][:T].reshape(T, G, dv)
+            for t in range(T):
+                slot = int(slot_mapping[t])
+                if slot >= 0:
+                    keys[slot // ps, :, slot % ps] = k[t]
+                    vals[slot // ps, :, slot % ps] = v[t]
+        rep = H // G
+        W, first = a["window"], a["keep_first"]
+        for t in range(T):
+            p = int(positions[t])
+            lo = max(0, p - W + 1) if W > 0 else 0
+            js = torch.tensor([j for j in range(p + 1) if j >= lo or j < first])
+            bt = block_tables[int(token_request[t])]
+            pg = bt[(js // ps).long()].long()
+            assert (pg >= 0).all(), "attention would read a page that is not held"
+            kk = keys[pg, :, (js % ps).long()].float()            # [n, G, dk]
+            vv = vals[pg, :, (js % ps).long()].float()
+            for h in range(H):
+                s = (kk[:, h // rep] @ q[t, h].float()) * a["scale"]
+                if a["sink"] is not None:
+                    s = torch.cat([s, a["sink"][h:h + 1]])
+                w = torch.softmax(s, 0)[: js.numel()]
+                a["out"][t, h * dv:(h + 1) * dv] = (w @ vv[:, h // rep]).to(a["out"].dtype)
+
+    def moe_route(self, a, T):
+        top, E = a["top_k"], a["logits"].shape[1]
+        s = torch.sigmoid(a["logits"][:T].float())
+        val, idx = torch.topk(s, top, dim=-1)
+        a["experts"][:T] = idx.to(torch.int32)
+        a["weights"][:T] = val / (val.sum(-1, keepdim=True) + 1e-20) * a["scale"]
+        flat = idx.reshape(-1)
+        order = torch.argsort(flat, stable=True)
+        a["order"][:T * top] = order.to(torch.int32)
+        counts = torch.bincount(flat, minlength=E)
+        a["offsets"][1:] = torch.cumsum(counts, 0).to(torch.int32)
+        a["offsets"][0] = 0
+
+    def grouped_linear(self, a, T):
+        top, w = a["top_k"], a["w"]
+        off, order = a["offsets"].tolist(), a["order"]
+        for e in range(w.shape[0]):
+            for r in range(off[e], off[e + 1]):
+                pair = int(order[r])
+                row = a["x"][pair // top if a["gather"] else r].float()
+                y = w[e].float() @ row
+                if a["act"]:
+                    n = y.numel() // 2
+                    g, u = y[:n].to(a["x"].dtype).float(), y[n:].to(a["x"].dtype).float()
+                    y = g * torch.sigmoid(g) * u
+                a["out"][pair if a["scatter"] else r] = y.to(a["out"].dtype)
+
     def token_side(self, a, T, token_ids):
         x = a["x"][:T]
         x += a["a"][:T].float() + (a["b"][:T].float() if a["b"] is not None else 0.0)
@@ -210,7 +303,24 @@ class HostPlan:
                     o.linear(a["x"][:n], a["w"], batch.logits if a["out"] is None else a["out"][:n])
             elif k == "linear_swiglu":
                 o.linear(a["x"][:T], a["w_gate_up"], a["gate_up"][:T])
-                o.swiglu(a["gate_up"][:T], a["out"][:T])
+                if a.get("act", "silu") == "silu":
+                    o.swiglu(a["gate_up"][:T], a["out"][:T])
+                else:
+                    o.gated_act(a["act"], a["params"], a["gate_up"][:T], a["out"][:T])
+            elif k == "postnorm":
+                o.postnorm(a["x"][:T], cut(a["y"]), a["gain"], a["eps"], a["accumulate"], cut(a["copy"]))
+            elif k == "window_attention":
+                g = batch.groups[a["group"]]
+                o.window_attention(a, T, batch.positions, batch.token_request, g.block_tables, g.slot_mapping, g.page_size)
+            elif k == "moe_route":
+                o.moe_route(a, T)
+            elif k == "grouped_linear":
+                o.grouped_linear(a, T)
+            elif k == "moe_combine":
+                top = a["weights"].shape[1]
+                y = a["y"][:T * top].view(T, top, -1)
+                v = (a["weights"][:T, :, None] * y).sum(1)
+                a["out"][:T] = v if a["base"] is None else a["base"][:T] + v
             elif k == "qkv_post":
                 self._qkv_post(a, batch, T)
             elif k == "attend":
