@@ -633,7 +633,7 @@ int op_window_attention(LlmeExecutor& ex, const LlmeWindowAttentionOp& o, const 
     if (int rc = ex.launched(post(&p, o.dtype, st), "window_post")) return rc;
     // bfloat16 with sizes the tensor-core kernel is built for: prompt portions in one launch, single tokens in another
     auto* tc = (WindowAttnTcFn)ex.find("window_attention_tc/" + std::to_string(o.dk) + "x" + std::to_string(o.dv));
-    if (tc && o.dtype == LLME_DT_BF16 && ex.choice("attention") == "fast" && g.page_size % 16 == 0) {
+    if (tc && o.dtype == LLME_DT_BF16 && ex.choice("attention") == "fast") {
         LlmeWindowFastArgs f = {};
         f.q = o.q; f.cache = o.cache; f.out = o.out; f.sink = o.sink; f.cu_q_lens = s.cu_q_lens; f.ctx_lens = s.ctx_lens;
         f.table_rows = s.state_slots; f.block_tables = g.block_tables; f.max_blocks = g.max_blocks; f.nh = o.nh; f.nkv = o.nkv;

@@ -1,7 +1,7 @@
-"""A design beside its closest existing model at equal size (`python bench.py --design bepuzen`).
+"""A design beside its closest existing model at equal size (`python bench.py --design bepuzen | torisun`).
 
 For each size: prefill of one 2,048-token prompt and decode at batch 1 / 8 / 64 over 2,048 cached tokens, tokens/s,
-for the latent-attention design and for the grouped-query model of the same width, depth and weight count per layer;
+for the design and for the grouped-query model of the same width, depth and (active) weight count per layer;
 and the time of every record of one layer of each (the model's own plan, record by record inside a CUDA graph, each
 layer's own weights, CUDA events) with the record's roofline: the larger of its algorithmic bytes over the copy
 bandwidth and its floating-point operations over the product peak, divided by the time measured.
@@ -38,7 +38,30 @@ def gqa_shape(layers: int, width: int, heads: int, inter: int, vocab: int = 3276
             "max_position_embeddings": 40960, "hidden_act": "silu"}
 
 
+def torisun_shape(layers: int, width: int, heads: int, kv_heads: int, ff: int, experts: int, top: int, expert_ff: int,
+                  window: int = 1024, keep_first: int = 4, dim: int = 128, vocab: int = 32768) -> Dict[str, Any]:
+    """Layers in pairs: one with keys and values of its own and the dense feed-forward, then one that reads the first
+    one's keys and values (with a narrower window) and has the mixture of experts with a shared expert."""
+    rot = {"base": 1000000.0, "dims": dim // 2, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    out = []
+    for i in range(layers):
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+             "mask": {"size": window if i % 2 == 0 else window // 2, "keep_first": keep_first}, "rot": rot}
+        if i % 2 == 0:
+            mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+        else:
+            m["kv_from"] = i - 1
+            mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "scale": 2.5},
+                   "shared": {"ff": expert_ff}}
+        out.append({"type": "attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Torisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
+
+
 # name -> (layers timed, the design's shape, the grouped-query model of the same width and feed-forward weight count)
+TORISUN_SIZES = {
+    "2048": (6, torisun_shape(6, 2048, 16, 4, 5504, 32, 4, 1024), gqa_shape(6, 2048, 16, 5504)),
+    "4096": (6, torisun_shape(6, 4096, 32, 8, 10944, 64, 4, 2048), gqa_shape(6, 4096, 32, 10944)),
+}
 SIZES = {
     "2048": (6, bepuzen_shape(6, 2048, 16, 8192), gqa_shape(6, 2048, 16, 5504)),
     "4096": (6, bepuzen_shape(6, 4096, 32, 16384), gqa_shape(6, 4096, 32, 10944)),
@@ -77,6 +100,36 @@ def record_cost(op, T: int, keys_per_row: float, cache_rows: float):
     if k in ("attention", "attend"):
         nh, nkv, hd = a["num_heads"], a["num_kv_heads"], a["head_dim"]
         return (f"attention {nh}/{nkv} heads of {hd}", 4.0 * T * nh * hd * keys_per_row, cache_rows * 2 * nkv * hd * el + 2 * T * nh * hd * el)
+    if k == "window_attention":
+        H, G, dk, dv, W, first = a["num_heads"], a["num_kv_heads"], a["qk_dim"], a["v_dim"], a["window"], a["keep_first"]
+        keys, rows_read = keys_per_row, cache_rows
+        if W:
+            ctx = 2 * keys_per_row - 1 if T > cache_rows / 2 else keys_per_row       # a prompt's mean is over positions 0..ctx-1
+            if T > cache_rows / 2:
+                n = int(ctx)
+                keys = (sum(min(i + 1, W) for i in range(n)) / n) + min(first, max(0, n - W))
+            else:
+                keys = min(keys_per_row, W + first)
+                rows_read = cache_rows * keys / keys_per_row
+        proj = a["q_in"].shape[1] + (a["k_in"].shape[1] + a["v_in"].shape[1] if a["k_in"] is not None else 0)
+        return (f"window attention {H}/{G} heads of {dk}/{dv}, window {W}+{first}" + ("" if a["k_in"] is not None else ", reads another layer's keys"),
+                2.0 * T * H * keys * (dk + dv), rows_read * G * (dk + dv) * el + T * (proj + 2 * H * dk + H * dv) * el)
+    if k == "postnorm":
+        D = a["x"].shape[1]
+        return "norm of a sublayer's output + residual add", 0.0, T * D * (4 + 4 + 4 + el)
+    if k == "moe_route":
+        E = a["logits"].shape[1]
+        return f"routing {a['top_k']} of {E}", 0.0, T * E * 4 + T * a["top_k"] * 12
+    if k == "grouped_linear":
+        w, top = a["w"], a["top_k"]
+        E, n, kk = w.shape
+        used = E * (1.0 - (1.0 - top / E) ** T)                       # experts that some token of the step uses, in the mean
+        n_out = n // 2 if a["act"] else n
+        return (f"grouped {'gate|up + silu' if a['act'] else 'down'} {E}x{n}x{kk}", 2.0 * T * top * n * kk,
+                used * n * kk * el + T * top * (kk * el + n_out * a["out"].element_size()))
+    if k == "moe_combine":
+        D, top = a["out"].shape[1], a["weights"].shape[1]
+        return "weighted sum of the chosen experts", 0.0, T * D * (top * 4 + (4 if a["base"] is not None else 0) + 4)
     if k == "rmsnorm":
         return "rmsnorm + residual add", 0.0, T * a["x"].shape[1] * (4 + 4 + 4 + el)
     if k == "token_side":
@@ -110,15 +163,16 @@ def layer_table(cfg, layers: int, batch: int, page: int, pk) -> Dict[str, List[D
     compiled = eng.ops.compile(plan)
     # which records belong to which layer: every block emits once more into a plan of its own, and is counted
     from .engine.plan import Plan
-    from .parts.base import emit_block
-    x = eng.rt.workspace("residual", eng.spec.hidden_size, torch.float32)
-    per_layer, at = [], 1
+    from .parts.base import emit_block, emit_embedding
+    scratch = Plan()
+    x = emit_embedding(scratch, eng.model.embedding, eng.spec.hidden_size)
+    per_layer, delta = [], None
     for i, run_ in enumerate(eng.model.order):
-        scratch = Plan()
-        emit_block(scratch, eng.model.blocks[run_.layer], x, None, eng._caches[i])
-        per_layer.append(list(range(at, at + len(scratch.ops))))
-        at += len(scratch.ops)
-    assert at + 2 == len(plan.ops), "the plan is not embedding, layers, final norm, head"
+        at = len(scratch.ops)
+        x, delta = emit_block(scratch, eng.model.blocks[run_.layer], x, delta, eng._caches[i])
+        per_layer.append(list(range(at, len(scratch.ops))))
+    assert len(scratch.ops) + 2 == len(plan.ops), "the plan is not embedding, layers, final norm, head"
+    assert all(a.kind == b.kind for a, b in zip(scratch.ops, plan.ops))
 
     def measure(indices, batch_obj, reps=10):
         eng.rt.batch = batch_obj
@@ -228,14 +282,16 @@ def run(args, pk) -> int:
     import gc
 
     import torch
-    sizes = [args.size] if getattr(args, "size", None) else list(SIZES)
-    rec: Dict[str, Any] = {"metric": "Bepuzen beside the grouped-query model of equal size, bf16: tokens/s and per-record rooflines",
+    design_name = getattr(args, "design", None) or "bepuzen"
+    table_of_sizes = {"bepuzen": SIZES, "torisun": TORISUN_SIZES}[design_name]
+    sizes = [args.size] if getattr(args, "size", None) else list(table_of_sizes)
+    rec: Dict[str, Any] = {"metric": f"{design_name.capitalize()} beside the grouped-query model of equal size, bf16: tokens/s and per-record rooflines",
                            "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic token ids, random weights",
                            "peaks": pk["source"], "page_size": args.page_size, "cached_tokens": CACHED, "sizes": {}}
     for name in sizes:
-        layers, design, closest = SIZES[name]
+        layers, design, closest = table_of_sizes[name]
         entry: Dict[str, Any] = {"layers": layers}
-        for label, cfg in (("bepuzen", design), ("gqa", closest)):
+        for label, cfg in ((design_name, design), ("gqa", closest)):
             entry[label] = throughput(cfg, [1, 8, 64], args.page_size, min(args.steps, 32), max(3, args.warmup))
             gc.collect()
             torch.cuda.empty_cache()
@@ -244,6 +300,6 @@ def run(args, pk) -> int:
             torch.cuda.empty_cache()
         rec["sizes"][name] = entry
     first = rec["sizes"][sizes[0]]
-    rec["value"] = first["bepuzen"][f"decode_b{8}"]["tokens_per_s"]
+    rec["value"] = first[design_name][f"decode_b{8}"]["tokens_per_s"]
     print(json.dumps(rec))
     return 0

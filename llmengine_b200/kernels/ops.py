@@ -184,8 +184,8 @@ class CudaOps:
 
     @staticmethod
     def window_tc_supports(qk_dim: int, v_dim: int, dtype: torch.dtype) -> bool:
-        """Whether the tensor-core window attention is built for this pair of sizes (bfloat16, multiples of 16 up to 256)."""
-        return dtype == torch.bfloat16 and qk_dim % 16 == 0 and v_dim % 16 == 0 and 16 <= qk_dim <= 256 and 16 <= v_dim <= 256
+        """Whether the tensor-core window attention is built for this pair of sizes (bfloat16, multiples of 16 up to 128)."""
+        return dtype == torch.bfloat16 and qk_dim % 16 == 0 and v_dim % 16 == 0 and 16 <= qk_dim <= 128 and 16 <= v_dim <= 128
 
     def decode_splits(self, requests: int, num_heads: int, num_kv_heads: int, head_dim: int, window: int, max_ctx: int) -> int:
         return int(self._xlib.llme_decode_splits(self._ex, requests, num_heads, num_kv_heads, head_dim, window, max_ctx))

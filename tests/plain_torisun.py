@@ -122,9 +122,17 @@ def route(h, w_router, top: int, scale: float):
     return idx, val / (val.sum(-1, keepdim=True) + 1e-20) * scale
 
 
-def moe_ff(h, w, pre, mlp, round_to):
+def routing_gaps(h, w_router, top: int) -> torch.Tensor:
+    """[T]: how far the last chosen expert's router logit lies above the first one not chosen (inf: all are chosen)."""
+    z = torch.sort(h @ w_router.t(), dim=-1, descending=True).values
+    return z[:, top - 1] - z[:, top] if top < z.shape[1] else torch.full((h.shape[0],), float("inf"))
+
+
+def moe_ff(h, w, pre, mlp, round_to, gaps=None):
     r = mlp["router"]
     idx, wt = route(h, w[pre + "router"], r["top"], r["scale"])
+    if gaps is not None:
+        gaps.append(routing_gaps(h, w[pre + "router"], r["top"]))
     out = torch.zeros(h.shape[0], w[pre + "e0.down"].shape[0])
     for e in range(r["experts"]):
         rows, slot = torch.nonzero(idx == e, as_tuple=True)
@@ -150,6 +158,7 @@ class PlainTorisun:
         pos = torch.arange(T)
         x = rms_norm(w["embed"][torch.tensor(list(ids), dtype=torch.long)], w["embed.norm"], eps)
         kv: Dict[int, tuple] = {}
+        gaps: list = []
         for i, L in enumerate(cfg["layers"]):
             m, pre = L["mixer"], f"l{i}.mix."
             h = _r(x, rt)
@@ -164,10 +173,12 @@ class PlainTorisun:
                 if mlp["kind"] == "dense":
                     y = dense_ff(h, w, f"l{i}.mlp.", mlp["limit"], rt)
                 else:
-                    y = moe_ff(h, w, f"l{i}.mlp.", mlp, rt)
+                    y = moe_ff(h, w, f"l{i}.mlp.", mlp, rt, gaps)
                 x = x + rms_norm(y, w[f"l{i}.norm2"], eps)
             if layers_out is not None:
                 layers_out.append(x.clone())
+        # per position, the closest call any router of the model made (a test may want to keep away from those)
+        self.gaps = torch.stack(gaps).min(0).values if gaps else torch.full((T,), float("inf"))
         return _r(rms_norm(x, w["final.norm"], eps), rt) @ w["embed"].t()
 
     def logits(self, ids: Sequence[int]) -> torch.Tensor:
