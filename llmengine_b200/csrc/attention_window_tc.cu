@@ -9,6 +9,10 @@
 // owns 16 rows: S = Q K^T with the queries kept in registers, the mask (j <= i and (i - j < window or j < keep_first)),
 // an online softmax whose running maximum starts at the sink and whose sum starts at one (the sink's own term), and
 // O += P V with the probabilities taken straight from the score registers.
+//
+// Single decoded tokens: a request's chunks are dealt out to `splits` blocks (a window of a thousand keys is seventeen
+// chunks, and eight requests of four key/value heads alone would leave most of the GPU idle); each writes its running
+// maximum, sum and unnormalised output per row to scratch memory, and a second kernel adds the parts and the sink.
 #include "common.cuh"
 #include "kernel_args.h"
 
@@ -59,7 +63,7 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
     pdl_wait();                                           // queries and the newest cache rows come from the kernel before
     const int req = a.rows[blockIdx.z];
     const int q0 = a.cu_q_lens[req], q_len = a.cu_q_lens[req + 1] - q0, ctx = a.ctx_lens[req], start = ctx - q_len;
-    const int G = a.nh / a.nkv, total_rows = q_len * G, tile0 = blockIdx.x * BM;
+    const int G = a.nh / a.nkv, total_rows = q_len * G, tile0 = a.splits > 1 ? 0 : blockIdx.x * BM;
     if (tile0 >= total_rows) return;
     const int kvh = blockIdx.y, ps = a.page_size;
     const int last_row = min(total_rows, tile0 + BM) - 1;
@@ -70,6 +74,11 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
     const int cw = lo_min / BN, c_end = p_hi / BN;
     const int nf = min((first_eff + BN - 1) / BN, cw);
     const int n_chunks = nf + (c_end - cw + 1);
+    // with splits, blockIdx.x is not a row tile (there is one) but a share of the chunks
+    const bool split = a.splits > 1;
+    const int per = split ? (n_chunks + a.splits - 1) / a.splits : n_chunks;
+    const int c_first = split ? min(n_chunks, (int)blockIdx.x * per) : 0;
+    const int c_stop = split ? min(n_chunks, c_first + per) : n_chunks;
     const int* bt = a.block_tables + (size_t)a.table_rows[req] * a.max_blocks;
     const size_t page_elems = (size_t)a.nkv * ps * (DK + DV);
     const bf16* cache = (const bf16*)a.cache;
@@ -131,8 +140,9 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
     for (int h = 0; h < 2; ++h) {
         const int row = tile0 + warp * 16 + (lane >> 2) + h * 8;
         const int head = kvh * G + (valid[h] ? row % G : 0);
-        m[h] = a.sink ? a.sink[head] * LOG2E : -INFINITY;  // the sink: a score that is not scaled and has no value
-        l[h] = a.sink ? 1.0f : 0.0f;
+        const bool with_sink = a.sink && !split;          // (with splits the second kernel adds it)
+        m[h] = with_sink ? a.sink[head] * LOG2E : -INFINITY;  // the sink: a score that is not scaled and has no value
+        l[h] = with_sink ? 1.0f : 0.0f;
     }
     float o[DV / 8][4];
 #pragma unroll
@@ -141,9 +151,9 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
         for (int i = 0; i < 4; ++i) o[n][i] = 0.0f;
 
     auto chunk_at = [&](int i) { return i < nf ? i : cw + (i - nf); };
-    load_chunk(0, chunk_at(0));
-    for (int ci = 0; ci < n_chunks; ++ci) {
-        if (ci + 1 < n_chunks) {
+    if (c_first < c_stop) load_chunk(c_first & 1, chunk_at(c_first));
+    for (int ci = c_first; ci < c_stop; ++ci) {
+        if (ci + 1 < c_stop) {
             load_chunk((ci + 1) & 1, chunk_at(ci + 1));
             cp_async_wait<1>();
         } else {
@@ -228,6 +238,25 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
         __syncthreads();
     }
 
+    if (split) {
+        // this share's part of every row: maximum, sum, unnormalised output
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (!valid[h]) continue;
+            const int row = warp * 16 + (lane >> 2) + h * 8;
+            float* part = a.scratch + ((((size_t)blockIdx.z * a.nkv + kvh) * a.splits + blockIdx.x) * G + row) * (DV + 2);
+            if ((lane & 3) == 0) {
+                part[0] = m[h];
+                part[1] = l[h];
+            }
+#pragma unroll
+            for (int n = 0; n < DV / 8; ++n) {
+                part[2 + n * 8 + (lane & 3) * 2] = o[n][h * 2];
+                part[2 + n * 8 + (lane & 3) * 2 + 1] = o[n][h * 2 + 1];
+            }
+        }
+        return;
+    }
     bf16* out = (bf16*)a.out;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -243,7 +272,48 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
     }
 }
 
+// One warp per row (a query head of a decoded token): the shares' parts and the sink become the output row.
+__global__ void __launch_bounds__(THREADS) window_merge_kernel(LlmeWindowFastArgs a) {
+    const int req = a.rows[blockIdx.y], kvh = blockIdx.x, G = a.nh / a.nkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const size_t token = a.cu_q_lens[req];
+    const float LOG2E = 1.4426950408889634f;
+    for (int row = warp; row < G; row += THREADS / 32) {
+        const int head = kvh * G + row;
+        const float* parts = a.scratch + (((size_t)blockIdx.y * a.nkv + kvh) * a.splits * G + row) * (DV + 2);
+        const size_t stride = (size_t)G * (DV + 2);
+        float m = a.sink ? a.sink[head] * LOG2E : -INFINITY;
+        for (int s = 0; s < a.splits; ++s) m = fmaxf(m, parts[s * stride]);
+        const float base = m == -INFINITY ? 0.0f : m;
+        float l = a.sink ? exp2f(a.sink[head] * LOG2E - base) : 0.0f;
+        float acc[(DV + 31) / 32];
+#pragma unroll
+        for (int i = 0; i < (DV + 31) / 32; ++i) acc[i] = 0.0f;
+        for (int s = 0; s < a.splits; ++s) {
+            const float* p = parts + s * stride;
+            const float w = exp2f(p[0] - base);           // a share that saw nothing: exp2(-inf) = 0
+            l += p[1] * w;
+#pragma unroll
+            for (int i = 0; i < (DV + 31) / 32; ++i) {
+                const int d = lane + 32 * i;
+                if (d < DV) acc[i] += p[2 + d] * w;
+            }
+        }
+        const float inv = 1.0f / l;
+        bf16* op = (bf16*)a.out + (token * a.nh + head) * DV;
+#pragma unroll
+        for (int i = 0; i < (DV + 31) / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < DV) op[d] = __float2bfloat16_rn(acc[i] * inv);
+        }
+    }
+}
+
 }  // namespace
+
+LLME_API long long llme_window_attention_tc_scratch_floats(int n_rows, int nh, int splits) {
+    return splits > 1 ? (long long)n_rows * nh * splits * (DV + 2) : 0;
+}
 
 LLME_API int llme_window_attention_tc_sizes(int* dk, int* dv) {
     *dk = DK;
@@ -270,6 +340,18 @@ LLME_API int llme_window_attention_tc(const LlmeWindowFastArgs* args, int max_q_
     }
     const int G = a.nh / a.nkv;
     const long long tiles = ((long long)max_q_len * G + BM - 1) / BM;
+    if (a.splits > 1) {
+        if (max_q_len != 1 || G > BM || !a.scratch) LLME_REFUSE("window attention: key ranges are for single tokens of at most %d heads a group, with scratch memory", BM);
+        llme_launch(window_tc_kernel, dim3((unsigned)a.splits, a.nkv, a.n_rows), dim3(THREADS), (size_t)SMEM_BYTES, stream, a);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            snprintf(llme_error_buffer(), 512, "%s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        // (an ordinary launch: it must not begin before every share has written its part)
+        window_merge_kernel<<<dim3(a.nkv, a.n_rows), dim3(THREADS), 0, stream>>>(a);
+        LLME_LAUNCH_STATUS();
+    }
     llme_launch(window_tc_kernel, dim3((unsigned)tiles, a.nkv, a.n_rows), dim3(THREADS), (size_t)SMEM_BYTES, stream, a);
     LLME_LAUNCH_STATUS();
 }

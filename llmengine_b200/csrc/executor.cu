@@ -644,7 +644,17 @@ int op_window_attention(LlmeExecutor& ex, const LlmeWindowAttentionOp& o, const 
         }
         if (s.num_decode > 0) {
             f.rows = s.decode_rows; f.n_rows = s.num_decode;
+            // key ranges: enough blocks for two an SM, no range shorter than two chunks of 64 keys, at most 8
+            long long keys = s.max_decode_ctx;
+            if (o.window > 0 && keys > (long long)o.window + o.keep_first) keys = (long long)o.window + o.keep_first;
+            const long long chunks = keys / 64 + 1, units = (long long)s.num_decode * o.nkv;
+            long long splits = (2LL * ex.sms + units - 1) / units;
+            if (splits > chunks / 2) splits = chunks / 2;
+            if (splits > 8) splits = 8;
+            if (splits < 2 || o.nh / o.nkv > 64 || !o.scratch || (long long)s.num_decode * o.nh * splits * (o.dv + 2) > o.scratch_floats) splits = 1;
+            f.splits = (int)splits; f.scratch = o.scratch;
             if (int rc = ex.launched(tc(&f, 1, s.max_decode_ctx, st), "window_attention_tc")) return rc;
+            if (splits > 1) ++ex.launches;
         }
         return 0;
     }

@@ -98,6 +98,7 @@ typedef struct LlmeWindowFastArgs {
     const int* rows; const int* cu_q_lens; const int* ctx_lens; const int* table_rows; const int* block_tables;
     int max_blocks, n_rows, nh, nkv, page_size, window, keep_first;
     float scale;
+    float* scratch; int splits;      /* single tokens: each request's keys cut into `splits` ranges whose parts meet in `scratch` */
 } LlmeWindowFastArgs;
 
 /* Routing of a mixture of experts (csrc/moe.cu). */

@@ -150,7 +150,7 @@ class Plan:
 
     def window_attention(self, *, q_in, k_in, v_in, q_gain, k_gain, eps: float, inv_freq, rot_dims: int, amplitude: float,
                          q, out, cache, group: int, num_heads: int, num_kv_heads: int, qk_dim: int, v_dim: int,
-                         window: int, keep_first: int, scale: float, sink=None) -> None:
+                         window: int, keep_first: int, scale: float, sink=None, scratch=None) -> None:
         """Grouped-query attention over a cache whose keys are `qk_dim` and whose values are `v_dim` wide, from the raw
         projections: q_in [T, H qk_dim] and, for a layer that stores, k_in [T, G qk_dim] and v_in [T, G v_dim] (column
         ranges of one product).  With gains, queries and keys are RMS-normed over the WHOLE projection (all heads at
@@ -158,11 +158,12 @@ class Plan:
         pairs by position * inv_freq[i], cosine and sine times `amplitude` (inv_freq None: no rotation); keys and
         values are stored.  Then query i sees key j if j <= i and (i - j < window or j < keep_first) (window 0: every
         earlier key); score = q . k * scale; softmax whose denominator also holds exp(sink_h) when `sink` [H] is given;
-        out [T, H v_dim].  `q` [T, H qk_dim] is the workspace of the finished queries."""
+        out [T, H v_dim].  `q` [T, H qk_dim] is the workspace of the finished queries; `scratch` (32-bit) is where the
+        parts of single tokens meet whose keys a kernel cuts into ranges."""
         self._add("window_attention", q_in=q_in, k_in=k_in, v_in=v_in, q_gain=q_gain, k_gain=k_gain, eps=float(eps),
                   inv_freq=inv_freq, rot_dims=int(rot_dims), amplitude=float(amplitude), q=q, out=out, cache=cache, group=group,
                   num_heads=num_heads, num_kv_heads=num_kv_heads, qk_dim=qk_dim, v_dim=v_dim, window=int(window),
-                  keep_first=int(keep_first), scale=float(scale), sink=sink)
+                  keep_first=int(keep_first), scale=float(scale), sink=sink, scratch=scratch)
 
     def moe_route(self, *, logits, top_k: int, scale: float, experts, weights, offsets, order, counts) -> None:
         """Routing of every token of the step from its router `logits` [T, E] (32-bit): scores = sigmoid(logits); the

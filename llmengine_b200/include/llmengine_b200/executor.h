@@ -213,6 +213,7 @@ typedef struct LlmeWindowAttentionOp {
     void* cache; int group;
     int nh, nkv, dk, dv, window, keep_first; float scale;
     const float* sink;
+    float* scratch; long long scratch_floats;                /* for single tokens whose keys are cut into ranges, or NULL */
 } LlmeWindowAttentionOp;
 
 /* Routing of a mixture of experts: sigmoid scores, the top_k largest, weights = chosen scores / their sum * scale;

@@ -137,7 +137,8 @@ class WindowAttentionOp(Structure):
                 ("v_stride", c_longlong), ("dtype", c_int), ("q_gain", c_void_p), ("k_gain", c_void_p), ("eps", c_float),
                 ("inv_freq", c_void_p), ("rot_dims", c_int), ("amplitude", c_float), ("q", c_void_p), ("out", c_void_p),
                 ("cache", c_void_p), ("group", c_int), ("nh", c_int), ("nkv", c_int), ("dk", c_int), ("dv", c_int),
-                ("window", c_int), ("keep_first", c_int), ("scale", c_float), ("sink", c_void_p)]
+                ("window", c_int), ("keep_first", c_int), ("scale", c_float), ("sink", c_void_p), ("scratch", c_void_p),
+                ("scratch_floats", c_longlong)]
 
 
 class MoeRouteOp(Structure):
@@ -330,7 +331,7 @@ def records(op, keep: List[Any]):
             qi.data_ptr(), ptr(ki), ptr(vi), qi.stride(0), ki.stride(0) if ki is not None else 0, vi.stride(0) if vi is not None else 0,
             code(qi.dtype), ptr(a["q_gain"]), ptr(a["k_gain"]), a["eps"], ptr(a["inv_freq"]), a["rot_dims"], a["amplitude"],
             q.data_ptr(), out.data_ptr(), cache.data_ptr(), a["group"], H, G, dk, dv, a["window"], a["keep_first"], a["scale"],
-            ptr(a["sink"]))
+            ptr(a["sink"]), ptr(a.get("scratch")), a["scratch"].numel() if a.get("scratch") is not None else 0)
     if k == "moe_route":
         z, ex_, wt, off, order, counts = a["logits"], a["experts"], a["weights"], a["offsets"], a["order"], a["counts"]
         assert z.dtype == wt.dtype == torch.float32 and z.stride(1) == 1 and ex_.is_contiguous() and wt.is_contiguous()

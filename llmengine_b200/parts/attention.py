@@ -225,7 +225,10 @@ class WindowSinkAttention(Part):
             inv_freq=pos.frequencies() if pos is not None else None, rot_dims=pos.dims if pos is not None else 0,
             amplitude=pos.amplitude if pos is not None else 1.0, q=q, out=out, cache=cache.kv, group=cache.group,
             num_heads=self.nh, num_kv_heads=self.nkv, qk_dim=self.dk, v_dim=self.dv, window=self.window,
-            keep_first=self.keep_first, scale=self.scale, sink=self.sink)
+            keep_first=self.keep_first, scale=self.scale, sink=self.sink,
+            # up to 8 key ranges per decoded token: a maximum, a sum and an output row per range and head
+            scratch=(rt.buffer("window_attention_scratch", 1, rt.max_requests * self.nh * 8 * (self.dv + 2), torch.float32,
+                               exact=True).view(-1) if rt.dtype == torch.bfloat16 else None))
         delta = rt.workspace("mixer_out", self.hidden, torch.float32)
         plan.linear(out, self.w_o, delta)
         return delta

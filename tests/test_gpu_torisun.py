@@ -133,7 +133,8 @@ def _attention_case(ops, dtype, H, G, dk, dv, W, first, page, lens, cuts, sink=T
         _run(ops, lambda p: p.window_attention(
             q_in=rows[:, :qs], k_in=rows[:, qs:qs + ks], v_in=rows[:, qs + ks:], q_gain=q_gain.to(DEV), k_gain=k_gain.to(DEV), eps=eps,
             inv_freq=f.to(DEV) if rot else None, rot_dims=rot or 0, amplitude=amp, q=q, out=out, cache=cache, group=0, num_heads=H,
-            num_kv_heads=G, qk_dim=dk, v_dim=dv, window=W, keep_first=first, scale=scale, sink=sinks.to(DEV) if sink else None), batch)
+            num_kv_heads=G, qk_dim=dk, v_dim=dv, window=W, keep_first=first, scale=scale, sink=sinks.to(DEV) if sink else None,
+            scratch=torch.zeros(R * H * 8 * (dv + 2), device=DEV) if dtype == torch.bfloat16 else None), batch)
         outs.append((spans, out.float().cpu()))
     # the plain result, request by request over the whole sequence
     rt = lambda t: t.to(dtype).float()
@@ -159,12 +160,16 @@ def _attention_case(ops, dtype, H, G, dk, dv, W, first, page, lens, cuts, sink=T
     (3, 3, 20, 12, 17, 5, 8, 6, None),              # sizes only the plain kernel takes
     (6, 1, 16, 48, 0, 0, 16, None, None),           # no window, no rotation, six heads on one key/value head
     (2, 2, 128, 128, 33, 40, 32, 128, None),        # more kept first positions than the window is wide
+    (8, 2, 64, 64, 400, 70, 16, 32, None),          # long enough that single tokens' keys are cut into ranges
+    (4, 1, 32, 48, 0, 0, 64, 16, None),             # the same without a window
 ])
 def test_window_attention_kernels(kernels, dtype, tol, H, G, dk, dv, W, first, page, rot, scaling):
     """Portions that start inside a page, a window and the kept first positions; single tokens beside them; prompts
     shorter than the window; free pages hold NaN."""
     ops = _ops(kernels)
     lens, cuts = [150, 9, 1, 200, 131, 77], [149, 0, 0, 130, 130, 70]
+    if W == 400 or (W == 0 and dv == 48):
+        lens, cuts = [700, 9, 1, 650, 131, 77], [699, 0, 0, 649, 130, 70]
     got, want = _attention_case(ops, dtype, H, G, dk, dv, W, first, page, lens, cuts, rot=rot, scaling=scaling, seed=dk + W)
     assert torch.isfinite(got).all()
     assert float((got - want).abs().max()) < tol
