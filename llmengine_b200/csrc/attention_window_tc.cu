@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
     const int n_chunks = nf + (c_end - cw + 1);
     // with splits, blockIdx.x is not a row tile (there is one) but a share of the chunks
     const bool split = a.splits > 1;
+    if (split) pdl_launch_dependents();                   // the few blocks of the kernel that adds the parts may move in
     const int per = split ? (n_chunks + a.splits - 1) / a.splits : n_chunks;
     const int c_first = split ? min(n_chunks, (int)blockIdx.x * per) : 0;
     const int c_stop = split ? min(n_chunks, c_first + per) : n_chunks;
@@ -84,21 +85,27 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
     const bf16* cache = (const bf16*)a.cache;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
+    // Eight threads bring one row (its page is looked up once, 128 bytes of it go in one request), sixteen rows a pass.
+    const int ps_shift = (ps & (ps - 1)) == 0 ? __ffs(ps) - 1 : -1;
     auto load_chunk = [&](int stage, int chunk) {
         bf16* Ks = smem + stage * STAGE_ELEMS;
         bf16* Vs = Ks + BN * LDK;
         const int j0 = chunk * BN;
-        constexpr int KC = DK / 8, VC = DV / 8;
-        for (int i = threadIdx.x; i < BN * (KC + VC); i += THREADS) {
-            const int r = i / (KC + VC), c = i % (KC + VC);
+        constexpr int KC = DK / 8, VC = DV / 8, TPR = 8;
+        const int c0 = threadIdx.x % TPR;
+        for (int r = threadIdx.x / TPR; r < BN; r += THREADS / TPR) {
             const int j = j0 + r;
             const bool needed = j <= p_hi && (j >= lo_min || j < first_eff);
-            const int page = needed ? bt[j / ps] : -1;
+            const int blk = ps_shift >= 0 ? j >> ps_shift : j / ps;
+            const int page = needed ? bt[blk] : -1;
             const bool ok = page >= 0;
-            const int off = j % ps;
-            const bf16* base = cache + (ok ? (size_t)page * page_elems : 0);
-            if (c < KC) cp_async16(Ks + r * LDK + c * 8, ok ? base + ((size_t)kvh * ps + off) * DK + c * 8 : cache, ok);
-            else cp_async16(Vs + r * LDV + (c - KC) * 8, ok ? base + (size_t)a.nkv * ps * DK + ((size_t)kvh * ps + off) * DV + (c - KC) * 8 : cache, ok);
+            const int off = j - blk * ps;
+            const bf16* krow = ok ? cache + (size_t)page * page_elems + ((size_t)kvh * ps + off) * DK : cache;
+            const bf16* vrow = ok ? cache + (size_t)page * page_elems + (size_t)a.nkv * ps * DK + ((size_t)kvh * ps + off) * DV : cache;
+#pragma unroll
+            for (int c = c0; c < KC; c += TPR) cp_async16(Ks + r * LDK + c * 8, ok ? krow + c * 8 : cache, ok);
+#pragma unroll
+            for (int c = c0; c < VC; c += TPR) cp_async16(Vs + r * LDV + c * 8, ok ? vrow + c * 8 : cache, ok);
         }
         cp_async_commit();
     };
@@ -179,19 +186,30 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
                 mma_bf16(s[n + 1], qf[k], b2, b3);
             }
 
-        // scale, mask, running maximum
+        // scale, mask, running maximum; a chunk that every row of the tile sees whole needs no mask
+        const bool whole = last_row == tile0 + BM - 1 && j0 + BN - 1 <= p_lo && (W <= 0 || p_hi - j0 < W || j0 + BN <= a.keep_first);
         float mx[2] = {-INFINITY, -INFINITY};
+        if (whole) {
 #pragma unroll
-        for (int n = 0; n < BN / 8; ++n)
+            for (int n = 0; n < BN / 8; ++n)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int h = i >> 1;
-                const int j = j0 + n * 8 + (lane & 3) * 2 + (i & 1);
-                const bool see = valid[h] && j <= pos[h] && (W <= 0 || pos[h] - j < W || j < a.keep_first);
-                const float v = see ? s[n][i] * sc : -INFINITY;
-                s[n][i] = v;
-                mx[h] = fmaxf(mx[h], v);
-            }
+                for (int i = 0; i < 4; ++i) {
+                    s[n][i] *= sc;
+                    mx[i >> 1] = fmaxf(mx[i >> 1], s[n][i]);
+                }
+        } else {
+#pragma unroll
+            for (int n = 0; n < BN / 8; ++n)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int h = i >> 1;
+                    const int j = j0 + n * 8 + (lane & 3) * 2 + (i & 1);
+                    const bool see = valid[h] && j <= pos[h] && (W <= 0 || pos[h] - j < W || j < a.keep_first);
+                    const float v = see ? s[n][i] * sc : -INFINITY;
+                    s[n][i] = v;
+                    mx[h] = fmaxf(mx[h], v);
+                }
+        }
         float corr[2], base[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -274,6 +292,7 @@ __global__ void __launch_bounds__(THREADS) window_tc_kernel(LlmeWindowFastArgs a
 
 // One warp per row (a query head of a decoded token): the shares' parts and the sink become the output row.
 __global__ void __launch_bounds__(THREADS) window_merge_kernel(LlmeWindowFastArgs a) {
+    pdl_wait();                                           // every share has written its part
     const int req = a.rows[blockIdx.y], kvh = blockIdx.x, G = a.nh / a.nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const size_t token = a.cu_q_lens[req];
@@ -348,8 +367,7 @@ LLME_API int llme_window_attention_tc(const LlmeWindowFastArgs* args, int max_q_
             snprintf(llme_error_buffer(), 512, "%s", cudaGetErrorString(e));
             return (int)e;
         }
-        // (an ordinary launch: it must not begin before every share has written its part)
-        window_merge_kernel<<<dim3(a.nkv, a.n_rows), dim3(THREADS), 0, stream>>>(a);
+        llme_launch(window_merge_kernel, dim3(a.nkv, a.n_rows), dim3(THREADS), 0, stream, a);
         LLME_LAUNCH_STATUS();
     }
     llme_launch(window_tc_kernel, dim3((unsigned)tiles, a.nkv, a.n_rows), dim3(THREADS), (size_t)SMEM_BYTES, stream, a);

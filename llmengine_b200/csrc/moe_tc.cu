@@ -2,10 +2,12 @@
 // expert over the (token, choice) pairs that were routed to it, rows gathered by token on the way in and scattered by
 // pair on the way out where asked, silu(gate) * up in the epilogue of the gate|up product.
 //
-// A block owns a tile of BM pairs of ONE expert x BN output columns and walks K in steps of 32 through a two-stage
-// cp.async pipeline; its four warps share the tile by columns (mma.sync m16n8k16, fragments by ldmatrix).  Two shapes:
-// 64 x 64 where experts get many rows (prompts), 16 x 128 where they get a few (decode steps: every weight tile is
-// then read by exactly one block, which is all a weight-streaming product can ask for).  The row tiles of all experts
+// A block owns a tile of BM pairs of ONE expert x BN output columns and walks K in steps of 32 through a cp.async
+// pipeline of two or three stages; its four warps share the tile by columns (mma.sync m16n8k16, fragments by ldmatrix).
+// Two shapes: 64 x 64 where experts get many rows (prompts; tiles of 128 rows on eight warps were no faster, 406 against
+// 372 us for 2,048 tokens on 4 of 32 experts of 1,024: an expert's last tile is the emptier the larger the tiles are),
+// 16 x 128 where they get a few (decode steps: every weight tile is then read by exactly one block, which is all a
+// weight-streaming product can ask for).  The row tiles of all experts
 // are numbered one after the other and a block finds its expert from the offsets; a launch has as many row tiles as
 // any routing can need, and blocks beyond the step's own count leave at once.  A row's sums never depend on which
 // other rows share its tile.
@@ -17,7 +19,7 @@ LLME_API const char* llme_last_error() { return llme_error_buffer(); }
 namespace {
 
 typedef __nv_bfloat16 bf16;
-constexpr int BK = 32, LDS = BK + 8, THREADS = 128;
+constexpr int BK = 32, LDS = BK + 8;
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
@@ -64,12 +66,15 @@ template <> __device__ __forceinline__ void store2<bf16>(bf16* p, float a, float
     if (two) p[1] = __float2bfloat16_rn(b);
 }
 
-// BM x BN tile; ACT: the weight rows of a column are its gate row and, n_out further on, its up row.
-template <int BM, int BN, bool ACT, typename O>
-__global__ void __launch_bounds__(THREADS) grouped_tc_kernel(LlmeGroupedArgs a) {
-    constexpr int MT = BM / 16, WN = BN / 4, NT = WN / 8, HALVES = ACT ? 2 : 1;
-    __shared__ __align__(16) bf16 As[2][BM][LDS];
-    __shared__ __align__(16) bf16 Bs[2][HALVES][BN][LDS];
+// BM x BN tile on WM x WNW warps, STAGES stages; ACT: the weight rows of a column are its gate row and, n_out further on, its up row.
+template <int BM, int BN, int WM, int WNW, int STAGES, bool ACT, typename O>
+__global__ void __launch_bounds__(32 * WM * WNW) grouped_tc_kernel(LlmeGroupedArgs a) {
+    constexpr int THREADS = 32 * WM * WNW, MT = BM / WM / 16, WN = BN / WNW, NT = WN / 8, HALVES = ACT ? 2 : 1;
+    constexpr int A_STAGE = BM * LDS, B_STAGE = HALVES * BN * LDS;
+    static_assert(MT >= 1 && NT >= 2 && NT % 2 == 0, "warp tiles are whole 16 x 16 pieces");
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* As = reinterpret_cast<bf16*>(smem_raw);                      // [STAGES][BM][LDS]
+    bf16* Bs = As + STAGES * A_STAGE;                                  // [STAGES][HALVES][BN][LDS]
     __shared__ int s_tile[3];
     __shared__ int s_src[BM], s_dst[BM];
     pdl_launch_dependents();
@@ -93,20 +98,25 @@ __global__ void __launch_bounds__(THREADS) grouped_tc_kernel(LlmeGroupedArgs a) 
     const bf16* x = (const bf16*)a.x;
     const bf16* w = (const bf16*)a.w + (size_t)e * a.w_expert;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = warp / WNW, wn = warp % WNW;
+    const int steps = (a.k + BK - 1) / BK;
 
-    auto load_stage = [&](int stage, int k0) {
-        for (int i = threadIdx.x; i < BM * (BK / 8); i += THREADS) {
-            const int r = i / (BK / 8), c = (i % (BK / 8)) * 8;
-            const int src = s_src[r];
-            const bool ok = src >= 0 && k0 + c < a.k;
-            cp_async16(&As[stage][r][c], ok ? x + (size_t)src * a.ldx + k0 + c : x, ok);
+    auto load_stage = [&](int stage, int step) {
+        if (step < steps) {
+            const int k0 = step * BK;
+            for (int i = threadIdx.x; i < BM * (BK / 8); i += THREADS) {
+                const int r = i / (BK / 8), c = (i % (BK / 8)) * 8;
+                const int src = s_src[r];
+                const bool ok = src >= 0 && k0 + c < a.k;
+                cp_async16(As + stage * A_STAGE + r * LDS + c, ok ? x + (size_t)src * a.ldx + k0 + c : x, ok);
+            }
+            for (int i = threadIdx.x; i < HALVES * BN * (BK / 8); i += THREADS) {
+                const int half = i / (BN * (BK / 8)), r = (i / (BK / 8)) % BN, c = (i % (BK / 8)) * 8;
+                const bool ok = col0 + r < n_out && k0 + c < a.k;
+                cp_async16(Bs + stage * B_STAGE + (half * BN + r) * LDS + c, ok ? w + (size_t)(half * n_out + col0 + r) * a.ldw + k0 + c : w, ok);
+            }
         }
-        for (int i = threadIdx.x; i < HALVES * BN * (BK / 8); i += THREADS) {
-            const int half = i / (BN * (BK / 8)), r = (i / (BK / 8)) % BN, c = (i % (BK / 8)) * 8;
-            const bool ok = col0 + r < n_out && k0 + c < a.k;
-            cp_async16(&Bs[stage][half][r][c], ok ? w + (size_t)(half * n_out + col0 + r) * a.ldw + k0 + c : w, ok);
-        }
-        cp_async_commit();
+        cp_async_commit();                                // one group a step, also an empty one: the count below relies on it
     };
 
     float acc[HALVES][MT][NT][4];
@@ -119,29 +129,26 @@ __global__ void __launch_bounds__(THREADS) grouped_tc_kernel(LlmeGroupedArgs a) 
 #pragma unroll
                 for (int i = 0; i < 4; ++i) acc[h][m][n][i] = 0.0f;
 
-    const int steps = (a.k + BK - 1) / BK;
-    load_stage(0, 0);
+#pragma unroll
+    for (int s = 0; s < STAGES - 1; ++s) load_stage(s, s);
     for (int s = 0; s < steps; ++s) {
-        if (s + 1 < steps) {
-            load_stage((s + 1) & 1, (s + 1) * BK);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        const int st = s & 1;
+        cp_async_wait<STAGES - 2>();                      // the loads of step s have landed
+        __syncthreads();                                  // ... for every thread, and step s - 1 has been read by all
+        load_stage((s + STAGES - 1) % STAGES, s + STAGES - 1);
+        const bf16* At = As + (s % STAGES) * A_STAGE + wm * (BM / WM) * LDS;
+        const bf16* Bt = Bs + (s % STAGES) * B_STAGE;
 #pragma unroll
         for (int kk = 0; kk < BK; kk += 16) {
             unsigned af[MT][4];
 #pragma unroll
             for (int m = 0; m < MT; ++m)
-                ldmatrix_x4(af[m][0], af[m][1], af[m][2], af[m][3], &As[st][m * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+                ldmatrix_x4(af[m][0], af[m][1], af[m][2], af[m][3], At + (m * 16 + (lane & 15)) * LDS + kk + (lane >> 4) * 8);
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
 #pragma unroll
                 for (int n = 0; n < NT; n += 2) {
                     unsigned b0, b1, b2, b3;              // (n-tile n: k 0-7, k 8-15), (n-tile n + 1: k 0-7, k 8-15)
-                    ldmatrix_x4(b0, b1, b2, b3, &Bs[st][h][warp * WN + n * 8 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+                    ldmatrix_x4(b0, b1, b2, b3, Bt + (h * BN + wn * WN + n * 8 + (lane & 7) + (lane >> 4) * 8) * LDS + kk + ((lane >> 3) & 1) * 8);
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
                         mma_bf16(acc[h][m][n], af[m], b0, b1);
@@ -149,7 +156,6 @@ __global__ void __launch_bounds__(THREADS) grouped_tc_kernel(LlmeGroupedArgs a) 
                     }
                 }
         }
-        __syncthreads();
     }
 
     O* out = (O*)a.out;
@@ -157,12 +163,12 @@ __global__ void __launch_bounds__(THREADS) grouped_tc_kernel(LlmeGroupedArgs a) 
     for (int m = 0; m < MT; ++m)
 #pragma unroll
         for (int half_rows = 0; half_rows < 2; ++half_rows) {
-            const int r = m * 16 + (lane >> 2) + half_rows * 8;
+            const int r = wm * (BM / WM) + m * 16 + (lane >> 2) + half_rows * 8;
             const int dst = s_dst[r];
             if (dst < 0) continue;
 #pragma unroll
             for (int n = 0; n < NT; ++n) {
-                const int col = col0 + warp * WN + n * 8 + (lane & 3) * 2;
+                const int col = col0 + wn * WN + n * 8 + (lane & 3) * 2;
                 if (col >= n_out) continue;
                 float v0 = acc[0][m][n][half_rows * 2], v1 = acc[0][m][n][half_rows * 2 + 1];
                 if (ACT) {
@@ -178,8 +184,9 @@ __global__ void __launch_bounds__(THREADS) grouped_tc_kernel(LlmeGroupedArgs a) 
         }
 }
 
-template <int BM, int BN, bool ACT, typename O>
+template <int BM, int BN, int WM, int WNW, int STAGES, bool ACT, typename O>
 int launch(const LlmeGroupedArgs& a, cudaStream_t s) {
+    constexpr int SMEM = STAGES * (BM + (ACT ? 2 : 1) * BN) * LDS * (int)sizeof(bf16);
     const int n_out = ACT ? a.n / 2 : a.n;
     const int most = a.num_experts < a.pairs ? a.num_experts : a.pairs;
     int tiles = (a.pairs + BM - 1) / BM + most;           // every expert may add one tile that is not full
@@ -188,15 +195,24 @@ int launch(const LlmeGroupedArgs& a, cudaStream_t s) {
         snprintf(llme_error_buffer(), 512, "grouped_linear_tc: %d row tiles exceed a launch", tiles);
         return -1;
     }
-    llme_launch(grouped_tc_kernel<BM, BN, ACT, O>, dim3((n_out + BN - 1) / BN, tiles), dim3(THREADS), 0, s, a);
+    auto kernel = grouped_tc_kernel<BM, BN, WM, WNW, STAGES, ACT, O>;
+    static bool configured = false;
+    if (!configured) {
+        if (SMEM > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+            snprintf(llme_error_buffer(), 512, "grouped_linear_tc: %d bytes of shared memory are not available", SMEM);
+            return -1;
+        }
+        configured = true;
+    }
+    llme_launch(kernel, dim3((n_out + BN - 1) / BN, tiles), dim3(32 * WM * WNW), (size_t)SMEM, s, a);
     LLME_LAUNCH_STATUS();
 }
 
 template <bool ACT, typename O>
 int dispatch(const LlmeGroupedArgs& a, cudaStream_t s) {
     // few rows per expert: tiles of 16 rows, so that little of a tile is padding and every weight is read once
-    if ((long long)a.pairs < 32LL * a.num_experts) return launch<16, 128, ACT, O>(a, s);
-    return launch<64, 64, ACT, O>(a, s);
+    if ((long long)a.pairs < 32LL * a.num_experts) return launch<16, 128, 1, 4, 4, ACT, O>(a, s);     // three steps of weights in flight per block
+    return launch<64, 64, 1, 4, 3, ACT, O>(a, s);
 }
 
 }  // namespace
