@@ -281,12 +281,77 @@ __global__ void postnorm_kernel(float* x, const Y* y, const G* __restrict__ gain
     }
 }
 
+// The same for 32-bit y in rows of whole 16-byte pieces: a row is read once and stays in registers between the sum of
+// squares and the update, 16 bytes a load.
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 v;
+    v.x = *reinterpret_cast<const unsigned*>(&lo);
+    v.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = v;
+}
+
+template <typename G, typename C, int V>
+__global__ void postnorm_vec_kernel(float* x, const float* y, const G* __restrict__ gain, C* __restrict__ copy, int cols, float eps,
+                                    int accumulate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * cols;
+    const int n4 = cols >> 2;
+    float4 v[V];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        v[i] = idx < n4 ? reinterpret_cast<const float4*>(y + base)[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)cols + eps);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+        const int idx = threadIdx.x + i * blockDim.x;
+        if (idx >= n4) continue;
+        float4 o = accumulate ? reinterpret_cast<const float4*>(x + base)[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const G* g = gain + 4 * idx;
+        o.x += (v[i].x * rinv) * to_f32(g[0]);
+        o.y += (v[i].y * rinv) * to_f32(g[1]);
+        o.z += (v[i].z * rinv) * to_f32(g[2]);
+        o.w += (v[i].w * rinv) * to_f32(g[3]);
+        reinterpret_cast<float4*>(x + base)[idx] = o;
+        if (copy) store4(copy + base + 4 * idx, o.x, o.y, o.z, o.w);
+    }
+}
+
+template <typename G, typename C>
+static void launch_postnorm_vec(float* x, const float* y, const void* gain, void* copy, int rows, int cols, float eps, int accumulate,
+                                cudaStream_t stream) {
+    const int n4 = cols / 4;
+    int threads = n4 < 1024 ? ((n4 + 31) / 32) * 32 : 1024;
+    if (n4 > 1024 && n4 <= 2048) threads = ((n4 / 2 + 31) / 32) * 32;
+    const int per = (n4 + threads - 1) / threads;
+    if (per <= 1) llme_launch(postnorm_vec_kernel<G, C, 1>, dim3(rows), dim3(threads), 0, stream, x, y, (const G*)gain, (C*)copy, cols, eps, accumulate);
+    else if (per <= 2) llme_launch(postnorm_vec_kernel<G, C, 2>, dim3(rows), dim3(threads), 0, stream, x, y, (const G*)gain, (C*)copy, cols, eps, accumulate);
+    else llme_launch(postnorm_vec_kernel<G, C, 4>, dim3(rows), dim3(threads), 0, stream, x, y, (const G*)gain, (C*)copy, cols, eps, accumulate);
+}
+
 LLME_API int llme_postnorm(float* x, const void* y, int y_dtype, const void* gain, int gain_dtype, void* copy, int copy_dtype,
                            int rows, int cols, float eps, int accumulate, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return 0;
     if (!x || (y && !gain) || (!y && !copy)) LLME_REFUSE("postnorm: null pointer");
     if (y && !(eps > 0.0f)) LLME_REFUSE("postnorm: eps must be positive");
     if (copy && copy_dtype != LLME_BF16 && copy_dtype != LLME_F32) LLME_REFUSE("postnorm: unsupported copy dtype %d", copy_dtype);
+    if (y && y_dtype == LLME_F32 && cols % 4 == 0 && cols <= 16384 && (((uintptr_t)x | (uintptr_t)y | (uintptr_t)copy) & 15) == 0 &&
+        (gain_dtype == LLME_F32 || gain_dtype == LLME_BF16)) {
+        const bool c32 = copy && copy_dtype == LLME_F32;
+        if (gain_dtype == LLME_F32 && c32) launch_postnorm_vec<float, float>(x, (const float*)y, gain, copy, rows, cols, eps, accumulate, stream);
+        else if (gain_dtype == LLME_F32) launch_postnorm_vec<float, __nv_bfloat16>(x, (const float*)y, gain, copy, rows, cols, eps, accumulate, stream);
+        else if (c32) launch_postnorm_vec<__nv_bfloat16, float>(x, (const float*)y, gain, copy, rows, cols, eps, accumulate, stream);
+        else launch_postnorm_vec<__nv_bfloat16, __nv_bfloat16>(x, (const float*)y, gain, copy, rows, cols, eps, accumulate, stream);
+        LLME_LAUNCH_STATUS();
+    }
     const int threads = cols >= 4096 ? 1024 : (cols >= 2048 ? 512 : (cols >= 1024 ? 256 : 128));
 #define LLME_PN(Y, G, C) llme_launch(postnorm_kernel<Y, G, C>, dim3(rows), dim3(threads), 0, stream, x, (const Y*)y, (const G*)gain, (C*)copy, cols, eps, accumulate)
 #define LLME_PN_C(Y, G) do { if (copy && copy_dtype == LLME_F32) LLME_PN(Y, G, float); else LLME_PN(Y, G, __nv_bfloat16); } while (0)
