@@ -166,7 +166,8 @@ static int launch_plain_v(const LlmeWindowAttnArgs& a, cudaStream_t s) {
     else if (regs <= 2) llme_launch(window_attention_plain_kernel<T, KR, 2>, dim3(grid), dim3(wpb * 32), 0, s, a);
     else if (regs <= 4) llme_launch(window_attention_plain_kernel<T, KR, 4>, dim3(grid), dim3(wpb * 32), 0, s, a);
     else if (regs <= 8) llme_launch(window_attention_plain_kernel<T, KR, 8>, dim3(grid), dim3(wpb * 32), 0, s, a);
-    else LLME_REFUSE("window attention: a value size of %d is larger than 256", a.dv);
+    else if (regs <= 16) llme_launch(window_attention_plain_kernel<T, KR, 16>, dim3(grid), dim3(wpb * 32), 0, s, a);
+    else LLME_REFUSE("window attention: a value size of %d is larger than 512", a.dv);
     LLME_LAUNCH_STATUS();
 }
 
@@ -177,7 +178,8 @@ static int launch_plain(const LlmeWindowAttnArgs& a, cudaStream_t s) {
     if (regs <= 2) return launch_plain_v<T, 2>(a, s);
     if (regs <= 4) return launch_plain_v<T, 4>(a, s);
     if (regs <= 8) return launch_plain_v<T, 8>(a, s);
-    LLME_REFUSE("window attention: a query/key size of %d is larger than 256", a.dk);
+    if (regs <= 16) return launch_plain_v<T, 16>(a, s);
+    LLME_REFUSE("window attention: a query/key size of %d is larger than 512", a.dk);
 }
 
 LLME_API int llme_window_attention_plain(const LlmeWindowAttnArgs* args, int dtype, cudaStream_t stream) {

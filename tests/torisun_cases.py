@@ -13,7 +13,7 @@ from helpers import (compare, engine_for, max_live_tokens, random_ids, replay, t
                      trace_portions, trace_whole)
 from plain_torisun import PlainTorisun
 
-TOL_F32 = 3e-4          # logits of these models are of order one to ten; only the order of sums differs
+TOL_F32 = 3e-4          # for logits of order one to ten (only the order of sums differs); it grows with larger ones
 
 
 def reference_logits(model_dir: str, reqs: Dict[str, List[int]], dtype: str):
@@ -28,10 +28,10 @@ def reference_logits(model_dir: str, reqs: Dict[str, List[int]], dtype: str):
     out) moves the logits by far more; the negative controls check that on the plain implementation."""
     plain = PlainTorisun(model_dir)
     rounded = PlainTorisun(model_dir, round_to=torch.bfloat16)
-    keep_away_from_close_calls(rounded if dtype == "bfloat16" else plain, reqs, 0.03 if dtype == "bfloat16" else 2e-4)
+    keep_away_from_close_calls(rounded if dtype == "bfloat16" else plain, reqs, 0.2 if dtype == "bfloat16" else 2e-4)
     ref = {r: plain.logits(ids) for r, ids in reqs.items()}
     if dtype != "bfloat16":
-        return ref, TOL_F32
+        return ref, TOL_F32 * max(1.0, max(float(v.abs().max()) for v in ref.values()) / 10.0)
     ref16 = {r: rounded.logits(ids) for r, ids in reqs.items()}
     inherent = max(float((ref16[r] - ref[r]).abs().max()) for r in ref)
     return ref16, max(5e-3, 1.5 * inherent)
