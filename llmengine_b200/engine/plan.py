@@ -157,7 +157,7 @@ class Plan:
         once, gain vectors of that size); the first `rot_dims` coordinates of every head are rotated in rotate-half
         pairs by position * inv_freq[i], cosine and sine times `amplitude` (inv_freq None: no rotation); keys and
         values are stored.  Then query i sees key j if j <= i and (i - j < window or j < keep_first) (window 0: every
-        earlier key); score = q . k * scale; softmax whose denominator also holds exp(sink_h) when `sink` [H] is given;
+        earlier key); s_ij = scale (q_i . k_j); p_ij = exp(s_ij) / (sum_j' exp(s_ij') [+ exp(sink_h) with `sink` [H]]);
         out [T, H v_dim].  `q` [T, H qk_dim] is the workspace of the finished queries; `scratch` (32-bit) is where the
         parts of single tokens meet whose keys a kernel cuts into ranges."""
         self._add("window_attention", q_in=q_in, k_in=k_in, v_in=v_in, q_gain=q_gain, k_gain=k_gain, eps=float(eps),
@@ -166,9 +166,9 @@ class Plan:
                   keep_first=int(keep_first), scale=float(scale), sink=sink, scratch=scratch)
 
     def moe_route(self, *, logits, top_k: int, scale: float, experts, weights, offsets, order, counts) -> None:
-        """Routing of every token of the step from its router `logits` [T, E] (32-bit): scores = sigmoid(logits); the
-        `top_k` largest are chosen (`experts` [T, top_k] int32, best first) with `weights` [T, top_k] = their scores
-        divided by their sum (+ 1e-20) times `scale`.  The (token, choice) pairs are then listed expert by expert:
+        """Routing of every token of the step from its router `logits` [T, E] (32-bit): s = sigmoid(logits); C = the
+        `top_k` experts of largest s (`experts` [T, top_k] int32, best first); `weights` [T, top_k]: w_e = scale * s_e /
+        (sum over C of s + 1e-20).  The (token, choice) pairs are then listed expert by expert:
         `offsets` [E + 1] int32 with the pairs of expert e at order[offsets[e] : offsets[e + 1]], a pair being
         token * top_k + choice.  `counts` [E] int32 is scratch that is zero between launches."""
         self._add("moe_route", logits=logits, top_k=int(top_k), scale=float(scale), experts=experts, weights=weights,

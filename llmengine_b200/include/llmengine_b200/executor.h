@@ -216,7 +216,7 @@ typedef struct LlmeWindowAttentionOp {
     float* scratch; long long scratch_floats;                /* for single tokens whose keys are cut into ranges, or NULL */
 } LlmeWindowAttentionOp;
 
-/* Routing of a mixture of experts: sigmoid scores, the top_k largest, weights = chosen scores / their sum * scale;
+/* Routing of a mixture of experts: s = sigmoid(logits), the top_k largest, w_e = scale * s_e / (sum of the chosen s + 1e-20);
  * the (token, choice) pairs listed expert by expert (csrc/moe.cu). */
 typedef struct LlmeMoeRouteOp {
     const float* logits; long long ld; int num_experts, top_k; float scale;

@@ -152,8 +152,8 @@ class WindowSinkAttention(Part):
       `dims` coordinates of every head), or None;
     * scores are scaled by `scale`;
     * query i sees key j if j <= i and (i - j < window or j < keep_first); window 0: every earlier key;
-    * with `sink`, a learned number per head whose exponential joins the softmax denominator (it has no key, no value
-      and is not scaled);
+    * with `sink`, one learned logit per head takes part in the softmax's normalisation only: p_j = exp(s_j) /
+      (exp(sink_h) + sum over visible keys of exp(s_j')); nothing is attended to through it and `scale` does not apply to it;
     * `own_kv` False: the layer has no key and value projections and reads the cache of the run that the layer order
       names (keys as stored there, normed and rotated); `retain_window` / `retain_first` then say what that cache
       keeps (the widest needs among the layers that read it), which may be more than this layer's own mask.

@@ -147,9 +147,9 @@ class GatedDense(Part):
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(Part):
     """A mixture of `num_experts` small feed-forwards down(silu(gate h) * (up h)) of which every token uses `top_k`:
-    router logits z = W_router h in 32-bit, scores sigmoid(z), the `top_k` largest chosen, weights = the chosen scores
-    divided by their sum (+ 1e-20) times `route_scale`; the output is the weighted sum of the chosen experts' outputs,
-    plus, with `shared_size` > 0, an expert of that size that every token uses.  Tensors: router; e<i>.gate / up /
+    z = W_router h in 32-bit, s = sigmoid(z), C = the `top_k` experts of largest s, w_e = route_scale * s_e / (sum over C
+    of s + 1e-20), output = sum over C of w_e expert_e(h), plus, with `shared_size` > 0, one more expert of that size that
+    takes every token with weight one.  Tensors: router; e<i>.gate / up /
     down; shared.gate / up / down.
 
     The experts' matrices are stacked ([E, 2 ff, D] and [E, D, ff]) and run as two grouped products over the

@@ -71,13 +71,13 @@ TINY_B = {
 }
 # wide enough for sharp attention over long contexts; pages of 64 and 16 put page edges inside and outside the windows
 TINY_C = {
-    "architecture": "Torisun", "vocab": 300, "width": 128, "norm": {"eps": 1e-6},
+    "architecture": "Torisun", "vocab": 300, "width": 128, "norm": {"eps": 2e-6},
     "layers": [
-        layer(mixer(8, 2, 64, 64, 0.125, 130, 70, base=1e6, dims=32, scaling={"factor": 2.0, "original": 256, "fast": 32.0, "slow": 1.0}),
-              dense(192, 1.5)),
-        layer(mixer(8, 2, 64, 64, 0.11, 64, 17, base=1e6, dims=32, scaling={"factor": 2.0, "original": 256, "fast": 32.0, "slow": 1.0},
-                    kv_from=0), moe(12, 3, 48, 2.0, shared=64)),
-        layer(mixer(4, 4, 32, 32, 0.18, 31, 0, base=1e4), moe(12, 3, 48, 2.0)),
+        layer(mixer(8, 2, 64, 64, 0.14, 130, 70, base=5e5, dims=32, scaling={"factor": 3.0, "original": 256, "fast": 24.0, "slow": 1.5}),
+              dense(192, 1.2)),
+        layer(mixer(8, 2, 64, 64, 0.11, 64, 17, base=5e5, dims=32, scaling={"factor": 3.0, "original": 256, "fast": 24.0, "slow": 1.5},
+                    kv_from=0), moe(12, 3, 48, 1.8, shared=64)),
+        layer(mixer(4, 4, 32, 32, 0.18, 31, 0, base=1e4), moe(12, 3, 48, 1.8)),
     ],
 }
 # one layer with one mechanism each
