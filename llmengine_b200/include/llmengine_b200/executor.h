@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define LLME_MAX_GROUPS 8
+#define LLME_MAX_GROUPS 32   /* every distinct (window, kept first positions) among a model's layers is a group */
 
 enum { LLME_DT_F32 = 0, LLME_DT_BF16 = 1 };
 

@@ -8,7 +8,7 @@ from typing import Any, Callable, Dict, List, Optional
 
 import torch
 
-MAX_GROUPS = 8
+MAX_GROUPS = 32
 F32, BF16 = 0, 1
 ROWS = {"tokens": 0, "logits": 1}
 (OP_EMBEDDING, OP_RMSNORM, OP_LINEAR, OP_LINEAR_SWIGLU, OP_QKV_POST, OP_ATTEND, OP_ATTENTION, OP_CALL, OP_LINEAR_ACT,

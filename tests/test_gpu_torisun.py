@@ -266,6 +266,18 @@ def test_replay_gpu(tmp_path, name, cfg, page, lens, dtype, kernels):
     print(f"replay {name} {dtype} {kernels}: share of the tolerance: " + ", ".join(f"{k} {v:.2f}" for k, v in worst.items()))
 
 
+def test_every_layer_with_a_mask_of_its_own(tmp_path):
+    """Ten layers whose windows and kept counts all differ are ten cache groups, each with block tables of its own that
+    give pages back at its own pace."""
+    cfg = {"architecture": "Torisun", "vocab": 70, "width": 32, "norm": {"eps": 1e-5},
+           "layers": [layer(mixer(2, 1, 16, 16, 0.3, 3 + 5 * i, i % 4, base=50.0, dims=8), None) for i in range(10)]}
+    d = make_torisun_dir(str(tmp_path / "m"), cfg, seed=2, sharpen=2.0)
+    for dtype in ("float32", "bfloat16"):
+        eng = engine_for(d, dtype, 256, page_size=8, max_requests=2, max_model_len=256)
+        assert len(eng.cache.groups) == 10
+        replay_all_schedules(d, cfg, dtype, [90, 17, 60, 5, 33], 8, None, DEV, only=("whole", "mixed"))
+
+
 def test_the_fused_and_tensor_core_kernels_serve_bfloat16(tmp_path):
     from llmengine_b200.engine.engine import StepEntry
     d = make_torisun_dir(str(tmp_path / "C"), TINY_C, seed=4)
